@@ -1,0 +1,144 @@
+"""Pipelined runtime on CPU/gloo against the single-process delayed-teacher oracle."""
+import copy
+from argparse import Namespace
+
+import pytest
+import torch
+from torch import nn
+
+from tests.helpers import run_ranks
+from tspipe_b200 import TSPipe, TSPipeMode
+from tspipe_b200.losses import byol_loss, ema_update, soft_target_kd
+from tspipe_b200.models.mlp import mlp_sequential, toy_student, toy_teacher
+from tspipe_b200.oracle import DelayedTeacherOracle
+
+KD_ARGS = Namespace(T=4.0, alpha=0.9)
+
+
+def _toy_batches(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(64, 3, 32, 32, generator=g), torch.randint(0, 10, (64,), generator=g)) for _ in range(n)]
+
+
+def _oracle_kd(n_steps, n_ubatch, bwd_split, **kw):
+    torch.manual_seed(0)
+    teacher, student = toy_teacher(), toy_student()
+    opt = torch.optim.SGD(student.parameters(), lr=0.05)
+    orc = DelayedTeacherOracle(student, teacher, opt, soft_target_kd, None, 1.0, kd=True, n_ubatch=n_ubatch,
+                               bwd_split=bwd_split, extra_args=KD_ARGS, **kw)
+    losses = [orc.step(x, x, y) for x, y in _toy_batches(n_steps)]
+    return losses, {k: v.detach().clone() for k, v in student.state_dict().items()}
+
+
+def test_toy_kd_two_process_pipeline_matches_oracle(tmp_path):
+    """Toy soft-target KD, two pipeline stages as two spawned CPU processes (gloo), batch 64 in four
+    microbatches, SGD lr 0.05, seed 0: losses and final student weights equal the oracle's."""
+    n_steps = 6
+    ref_losses, ref_state = _oracle_kd(n_steps, 4, 2)
+    torch.manual_seed(0)
+    teacher, student = toy_teacher(), toy_student()
+    opt = torch.optim.SGD(student.parameters(), lr=0.05)
+    cfg = {"model_split": {"online": [3, 2], "target": [5, 4]}, "runtime": {"num_ubatch": 4, "backend": "gloo", "timeout_s": 60},
+           "train": {"deferred_batch_norm": False}}
+    with pytest.warns(UserWarning):
+        tsp = TSPipe(student, teacher, None, opt, soft_target_kd, None, 1.0, str(tmp_path),
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False, extra_args=KD_ARGS,
+                     config=cfg, argv=["--ip", "127.0.0.1", "--rank", "0", "--num-nodes", "1"], device="cpu")
+    losses = []
+    for x, y in _toy_batches(n_steps):
+        l = tsp.feed(x, x, y)
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    assert len(losses) == n_steps
+    torch.testing.assert_close(torch.tensor(losses), torch.tensor(ref_losses), rtol=1e-5, atol=1e-6)
+    online, _ = tsp.state_dicts()
+    merged = {}
+    for st in online.values():
+        merged.update(st)
+    assert set(merged) == set(ref_state)
+    for k in ref_state:
+        torch.testing.assert_close(merged[k], ref_state[k], rtol=1e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+def _ssl_models(seed=0):
+    torch.manual_seed(seed)
+    online = mlp_sequential([48, 32, 32, 24, 16], batch_norm=True)
+    target = copy.deepcopy(online)
+    predictor = nn.Sequential(nn.Linear(16, 16), nn.ReLU(), nn.Linear(16, 16))
+    return online, target, predictor
+
+
+def _ssl_batches(n, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(24, 48, generator=g), torch.randn(24, 48, generator=g)) for _ in range(n)]
+
+
+def _ssl_rank(rank, world, cfg, n_steps):
+    online, target, predictor = _ssl_models()
+    opt = torch.optim.SGD(list(online.parameters()) + list(predictor.parameters()), lr=0.1, momentum=0.9)
+    tsp = TSPipe(online, target, predictor, opt, byol_loss, ema_update, 0.9, "", config=cfg, device="cpu")
+    losses = []
+    for i, (a, b) in enumerate(_ssl_batches(n_steps)):
+        if i == 3:
+            tsp.update_lr(0.05)
+            tsp.update_momentum(0.95)
+        l = tsp.feed(a, b)
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    on, tg = tsp.state_dicts()
+    return losses, on, tg
+
+
+def _ssl_oracle(n_steps, n_ubatch, bwd_split, skip=0, gpipe=False):
+    from tspipe_b200.batchnorm import DeferredBatchNorm
+    online, target, predictor = _ssl_models()
+    full = nn.Sequential(*list(online.children()), *list(predictor.children()))
+    opt = torch.optim.SGD(list(online.parameters()) + list(predictor.parameters()), lr=0.1, momentum=0.9)
+    orc = DelayedTeacherOracle(full, target, opt, byol_loss, ema_update, 0.9, kd=False, n_ubatch=n_ubatch,
+                               bwd_split=bwd_split, skip_staleness=skip, gpipe=gpipe)
+    n_t = len(list(target.parameters()))
+    orc_update = orc.update_fn
+    orc.update_fn = lambda m, on, tg: orc_update(m, on[:n_t], tg)
+    losses = []
+    for i, (a, b) in enumerate(_ssl_batches(n_steps)):
+        if i == 3:
+            for g in opt.param_groups:
+                g["lr"] = 0.05
+            orc.momentum = 0.95
+        losses.append(orc.step(a, b))
+    return losses, orc.final_teacher(), {k: v.detach() for k, v in full.state_dict().items()}
+
+
+@pytest.mark.parametrize("pp,n_ub,split,skip,gpipe", [(2, 2, 2, 0, False), (3, 2, 2, 0, False), (3, 3, 1, 1, False),
+                                                      (2, 2, 1, 0, True), (1, 2, 2, 0, False)])
+def test_ssl_momentum_pipeline_matches_oracle(pp, n_ub, split, skip, gpipe):
+    """BYOL-style run (BatchNorm, predictor, SGD momentum, EMA teacher, lr/momentum updates) in
+    launcher mode: the pipelined result equals the oracle with the one-step-delayed teacher."""
+    n_steps = 7
+    n_on, n_tg = 5 + 3, 5
+    from tspipe_b200.tspipe import default_balance
+    cfg = {"model_split": {"online": default_balance(n_on, pp), "target": default_balance(n_tg, pp)},
+           "runtime": {"num_ubatch": n_ub, "bwd_split": split, "backend": "gloo", "timeout_s": 60},
+           "optimizer": {"num_skip_initial_staleness": skip},
+           "gpipe_emulation": {"enabled": gpipe, "num_ubatch": n_ub},
+           "train": {"deferred_batch_norm": False}}
+    ref_losses, ref_teacher, ref_online = _ssl_oracle(n_steps, n_ub, split, skip, gpipe)
+    out = run_ranks(_ssl_rank, pp, cfg, n_steps)
+    losses = out[pp - 1][0]
+    assert len(losses) == n_steps
+    torch.testing.assert_close(torch.tensor(losses), torch.tensor(ref_losses), rtol=2e-5, atol=1e-6)
+    _, on, tg = out[0]
+    # teacher parameters: compare values in order (keys differ: the oracle has the full model)
+    got_t = [v for j in sorted(tg) for k, v in tg[j].items() if "running" not in k and "num_batches" not in k]
+    want_t = list(ref_teacher.values())
+    assert len(got_t) == len(want_t)
+    for a, b in zip(got_t, want_t):
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)
+    got_o = [v for j in sorted(on) for k, v in on[j].items() if "running" not in k and "num_batches" not in k]
+    want_o = [v for k, v in ref_online.items() if "running" not in k and "num_batches" not in k]
+    assert len(got_o) == len(want_o)
+    for a, b in zip(got_o, want_o):
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)

@@ -1,0 +1,102 @@
+"""Microbatch-aware batch normalisation.
+
+Behaviour of the reference layer (`tspipe/batchnorm.py:17-120`, converter `:122-154`): in
+training mode every micro-batch is normalised with its *own* batch statistics, while the
+per-channel ``sum`` / ``sum_squares`` / element count are accumulated over ``chunks``
+micro-batches and committed to ``running_mean`` / ``running_var`` once per mini-batch
+(exponential or cumulative average); evaluation mode uses the running statistics.
+
+The reference pays two extra full reductions over the activation per call (``input.sum`` and
+``(input**2).sum``, `:52-53`).  Here the accumulators are fed from the batch statistics the
+normalisation computes anyway: ``sum += n*mean`` and ``sum_squares += n*(var + mean^2)`` -
+one pass over the activation (on CUDA the sm_100a kernel in :mod:`tspipe_b200.ops.fused`
+emits them from its statistics pass; otherwise the statistics come back from the
+library call through scratch running buffers with momentum 1).
+"""
+from __future__ import annotations
+
+from typing import Optional, TypeVar, cast
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+from torch.nn.modules.batchnorm import _BatchNorm
+
+TModule = TypeVar("TModule", bound=nn.Module)
+
+
+class DeferredBatchNorm(_BatchNorm):
+    sum: Tensor
+    sum_squares: Tensor
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: Optional[float] = 0.1,
+                 affine: bool = True, chunks: int = 1) -> None:
+        super().__init__(num_features, eps, momentum, affine, track_running_stats=True)
+        self.register_buffer("sum", torch.zeros_like(self.running_mean))
+        self.register_buffer("sum_squares", torch.zeros_like(self.running_var))
+        self.register_buffer("_mb_mean", torch.zeros_like(self.running_mean), persistent=False)
+        self.register_buffer("_mb_var", torch.ones_like(self.running_var), persistent=False)
+        self.counter = 0
+        self.tracked = 0
+        self.chunks = chunks
+
+    def _check_input_dim(self, input: Tensor) -> None:
+        if input.dim() < 2:
+            raise ValueError(f"expected at least 2D input (got {input.dim()}D input)")
+
+    @torch.no_grad()
+    def _track(self, n: int) -> bool:
+        """Fold the statistics of the micro-batch just normalised (``_mb_mean`` and the unbiased
+        ``_mb_var`` over ``n`` elements per channel) into the mini-batch accumulators."""
+        mean = self._mb_mean
+        var_b = self._mb_var * ((n - 1) / n) if n > 1 else torch.zeros_like(self._mb_var)
+        self.sum.add_(mean, alpha=n)
+        self.sum_squares.add_((var_b + mean * mean), alpha=n)
+        self.counter += n
+        self.tracked += 1
+        return self.tracked == self.chunks
+
+    @torch.no_grad()
+    def _commit(self) -> None:
+        self.num_batches_tracked += 1
+        m = 1.0 / float(self.num_batches_tracked) if self.momentum is None else self.momentum
+        mean = self.sum / self.counter
+        var = self.sum_squares / self.counter - mean ** 2
+        self.running_mean.mul_(1 - m).add_(mean, alpha=m)
+        self.running_var.mul_(1 - m).add_(var, alpha=m)
+        self.sum.zero_()
+        self.sum_squares.zero_()
+        self.counter = 0
+        self.tracked = 0
+
+    def forward(self, input: Tensor) -> Tensor:  # type: ignore[override]
+        if not self.training:
+            return F.batch_norm(input, self.running_mean, self.running_var, self.weight, self.bias,
+                                training=False, momentum=0.0, eps=self.eps)
+        n = input.numel() // input.size(1)
+        out = F.batch_norm(input, self._mb_mean, self._mb_var, self.weight, self.bias,
+                           training=True, momentum=1.0, eps=self.eps)
+        if self._track(n):
+            self._commit()
+        return out
+
+    @classmethod
+    def convert_deferred_batch_norm(cls, module: TModule, chunks: int = 1) -> TModule:
+        """Recursively swap every running-stat ``_BatchNorm`` for a :class:`DeferredBatchNorm`
+        sharing its parameters and buffers."""
+        if isinstance(module, DeferredBatchNorm):
+            module.chunks = chunks
+            return cast(TModule, module)
+        out: nn.Module = module
+        if isinstance(module, _BatchNorm) and module.track_running_stats:
+            out = DeferredBatchNorm(module.num_features, module.eps, module.momentum, module.affine, chunks)
+            if module.affine:
+                out.register_parameter("weight", module.weight)
+                out.register_parameter("bias", module.bias)
+            out.register_buffer("running_mean", module.running_mean)
+            out.register_buffer("running_var", module.running_var)
+            out.register_buffer("num_batches_tracked", module.num_batches_tracked)
+            out.train(module.training)
+        for name, child in module.named_children():
+            out.add_module(name, cls.convert_deferred_batch_norm(child, chunks))
+        return cast(TModule, out)

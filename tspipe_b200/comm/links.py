@@ -1,0 +1,119 @@
+"""Stage-boundary tensor links over ``torch.distributed`` point-to-point.
+
+Replaces the reference's channel machinery - metadata RPC, agreement RPC, locked NCCL
+send/recv and a device-wide synchronize per transfer (`tspipe/communicator.py:243-308,
+570-678`) - with plain ordered p2p on a direction-private communicator:
+
+* the receiver posts its receives ahead of time, in the sender's (schedule-determined)
+  order, from an otherwise idle stream, and the compute stream later waits on the
+  transfer's completion event - no host synchronisation on either side;
+* tensor shapes are announced once per (link, net, shape-epoch) through the key-value
+  store, not per message.
+
+On CPU (gloo) the same code runs with host-blocking ``wait``.
+"""
+from __future__ import annotations
+
+import pickle
+from collections import deque
+from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+TensorSpec = Tuple[Tuple[int, ...], torch.dtype]
+
+
+class RecvHandle:
+    __slots__ = ("tensors", "works", "_stream", "_done")
+
+    def __init__(self, tensors: List[torch.Tensor], works: List[Any], stream):
+        self.tensors, self.works, self._stream, self._done = tensors, works, stream, False
+
+    def wait(self) -> List[torch.Tensor]:
+        """Make the *current* stream (or the host, on CPU) wait for the data."""
+        if not self._done:
+            for w in self.works:
+                w.wait()
+            if self._stream is not None:
+                cur = torch.cuda.current_stream()
+                for t in self.tensors:
+                    t.record_stream(cur)
+            self._done = True
+        return self.tensors
+
+
+class Link:
+    """One direction of one stage boundary, as seen from one of its two ranks."""
+
+    def __init__(self, group, peer: int, device: torch.device):
+        self.group, self.peer, self.device = group, peer, device
+        self.cuda = device.type == "cuda"
+        self.post_stream = torch.cuda.Stream(device) if self.cuda else None
+        self._pending: Deque[Tuple[List[Any], List[torch.Tensor]]] = deque()
+
+    # -- send ---------------------------------------------------------------------------------
+    def send(self, tensors: Sequence[torch.Tensor]) -> None:
+        """Enqueue sends ordered after the work already queued on the current stream."""
+        tensors = [t if t.is_contiguous() else t.contiguous() for t in tensors]
+        works = [dist.isend(t, self.peer, group=self.group) for t in tensors]
+        self._pending.append((works, tensors))
+        self._reap()
+
+    def _reap(self) -> None:
+        while self._pending and all(w.is_completed() for w in self._pending[0][0]):
+            self._pending.popleft()
+
+    def flush(self) -> None:
+        while self._pending:
+            works, _ = self._pending.popleft()
+            for w in works:
+                w.wait()
+
+    # -- receive ------------------------------------------------------------------------------
+    def post_recv(self, specs: Sequence[TensorSpec]) -> RecvHandle:
+        if self.cuda:
+            with torch.cuda.stream(self.post_stream):
+                bufs = [torch.empty(shape, dtype=dtype, device=self.device) for shape, dtype in specs]
+                works = [dist.irecv(b, self.peer, group=self.group) for b in bufs]
+            return RecvHandle(bufs, works, self.post_stream)
+        bufs = [torch.empty(shape, dtype=dtype) for shape, dtype in specs]
+        works = [dist.irecv(b, self.peer, group=self.group) for b in bufs]
+        return RecvHandle(bufs, works, None)
+
+
+class MetaBoard:
+    """Shape/structure announcements through the rendezvous store.
+
+    A sender publishes the pytree structure and tensor specs of what crosses a link the
+    first time it sends for a given ``(link, net, shape_epoch)``; the receiver blocks on the
+    key only then.  (The reference ships this metadata with every message by RPC,
+    `tspipe/communicator.py:84-99,251-267`.)"""
+
+    def __init__(self, store, replica: int):
+        self.store, self.replica = store, replica
+        self._sent: Dict[str, bytes] = {}
+        self._got: Dict[str, Any] = {}
+
+    def _key(self, link: str, net: str, epoch: int) -> str:
+        return f"meta/{self.replica}/{link}/{net}/{epoch}"
+
+    def publish(self, link: str, net: str, epoch: int, meta: Any) -> None:
+        key = self._key(link, net, epoch)
+        blob = pickle.dumps(meta)
+        prev = self._sent.get(key)
+        if prev is None:
+            self.store.set(key, blob)
+            self._sent[key] = blob
+        elif prev != blob:
+            raise RuntimeError(f"stage output structure changed within shape epoch {epoch} on {link}/{net}; "
+                               "feed batches of a different shape through a new shape epoch")
+
+    def cached(self, link: str, net: str, epoch: int) -> bool:
+        return self._key(link, net, epoch) in self._got
+
+    def fetch(self, link: str, net: str, epoch: int) -> Any:
+        key = self._key(link, net, epoch)
+        if key not in self._got:
+            self._got[key] = pickle.loads(self.store.get(key))
+        return self._got[key]

@@ -1,0 +1,753 @@
+"""Per-rank stage engine: one executor walking its own column of the schedule.
+
+What the reference spreads over seven role threads, a condition variable, eleven task types
+with spin-checked preconditions and ~5 host synchronisations per microbatch
+(`tspipe/gpu_worker.py:26-149,357-381,468-563`, `tspipe/gpu_task.py:89-834`) is here ONE
+loop per rank over :func:`tspipe_b200.schedule.batch_block`:
+
+* ``T`` / ``O``  forward one microbatch through the teacher / student partition
+  (`gpu_task.py:431-530`), input from the feeder (stage 0) or the upstream link, output to the
+  downstream link or the loss collector (last stage);
+* ``LOSS``      full-batch loss on the last stage and per-nano-batch output gradients
+  (`gpu_task.py:89-226`);
+* ``B``         backward of one nano-batch, input gradient to the upstream link
+  (`gpu_task.py:229-285`);
+* ``OPT``       data-parallel gradient sync, optimizer step, momentum-teacher update
+  (`gpu_task.py:322-417`).
+
+Ordering between compute, copies and transfers is expressed with CUDA streams and events
+only; the host never waits for the device except when the caller asks for a loss value.
+On CPU (gloo) the same loop runs with blocking transfers.
+"""
+from __future__ import annotations
+
+import contextlib
+import queue
+import threading
+import time
+import traceback
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..batch_ops import Batch, ScatterGatherFn, defaultScatterGatherFn
+from ..comm.links import Link, MetaBoard, RecvHandle
+from ..comm.topology import Topology
+from ..logger import Log
+from ..model_wrapper import TSPipeModelOutput
+from ..schedule import Op, OpKind, ScheduleSpec, batch_block
+from ..utils import pytree as pt
+from .state import FlatParams, corresponding_prefix
+
+
+# ---------------------------------------------------------------------------------------------
+# messages from the feeder (same process: queue.Queue; spawned worker: multiprocessing queue)
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class FeedMsg:
+    batch_id: int
+    views: Optional[List[Any]] = None          # [view_1, view_2] mini-batch data (stage 0 only)
+    labels: Any = None                         # last stage only (KD mode)
+    shape_epoch: int = 0
+    new_lr: Any = None                         # scalar or per-group list, applied at OPT(batch_id)
+    new_momentum: Optional[float] = None
+    force_step: bool = False                   # epoch boundary: step even if accumulation is incomplete
+    epoch: int = 0
+    ready_event: Any = None                    # CUDA event: device copies of `views` are complete
+
+
+@dataclass
+class StopMsg:
+    last_batch: int
+
+
+@dataclass
+class EpochMsg:
+    batch_id: int                              # the optimizer steps at this batch regardless of accumulation
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+# ---------------------------------------------------------------------------------------------
+# teacher update strategies
+# ---------------------------------------------------------------------------------------------
+class TeacherUpdater:
+    def step(self, momentum: float) -> None:
+        raise NotImplementedError
+
+
+class FrozenTeacher(TeacherUpdater):
+    def step(self, momentum: float) -> None:
+        return
+
+
+class CallbackTeacher(TeacherUpdater):
+    """The reference contract: ``fn(momentum, online_new_params, target_prev_params) -> list``
+    evaluated per partition (`gpu_task.py:403-406`), result copied into the live teacher."""
+
+    def __init__(self, fn: Callable, online: Sequence[nn.Parameter], target: Sequence[nn.Parameter]):
+        self.fn, self.online, self.target = fn, list(online), list(target)
+
+    @torch.no_grad()
+    def step(self, momentum: float) -> None:
+        new = self.fn(momentum, [p.detach() for p in self.online], [p for p in self.target])
+        for p, q in zip(self.target, new):
+            if q is not p:
+                p.copy_(q)
+
+
+class FlatEmaTeacher(TeacherUpdater):
+    """``t = m*t + (1-m)*s`` over flat buffers in one launch (CUDA: the sm_100a kernel, which
+    may read ``s`` through a peer pointer; CPU: one ``lerp_``)."""
+
+    def __init__(self, teacher: FlatParams, student_flat: torch.Tensor, segments=None, use_kernel: bool = False):
+        self.teacher, self.student_flat, self.segments, self.use_kernel = teacher, student_flat, segments, use_kernel
+
+    @torch.no_grad()
+    def step(self, momentum: float) -> None:
+        n = self.teacher.total
+        if self.use_kernel:
+            from ..ops import fused
+            fused.ema_update_(self.teacher.data, self.student_flat[:n], momentum)
+        else:
+            self.teacher.data.lerp_(self.student_flat[:n], 1.0 - momentum)
+
+
+class CrossStageEmaTeacher(TeacherUpdater):
+    """Momentum update when teacher and student are cut at different children: some of a teacher
+    stage's student counterparts live on other ranks (:mod:`tspipe_b200.runtime.ema_plan`).
+
+    Transfer path (any backend): every stage packs the runs other stages need, all exchanges of
+    the step go out as one batched point-to-point group on the replica's pipeline group, then the
+    runs are blended in.  Peer path (CUDA, same node): the student buffers are mapped into every
+    rank (:mod:`tspipe_b200.comm.peer`) and the sm_100a kernel reads the remote runs straight
+    over NVLink; the batched exchange then only carries one-element "my step is done" tokens."""
+
+    def __init__(self, topo: Topology, plan, teacher: FlatParams, student: FlatParams, peer_flats=None,
+                 use_kernel: bool = False):
+        self.topo, self.plan, self.teacher, self.student = topo, plan, teacher, student
+        self.peer_flats, self.use_kernel = peer_flats, use_kernel
+        self._seg_cache = None
+
+    def _rank(self, stage: int) -> int:
+        return self.topo.rank_of(self.topo.replica, stage)
+
+    @torch.no_grad()
+    def step(self, momentum: float) -> None:
+        plan, t, s = self.plan, self.teacher.data, self.student.data
+        peer = self.peer_flats is not None
+        ops, recv_bufs = [], {}
+        for dst, runs in sorted(plan.send.items()):
+            buf = s.new_zeros(1) if peer else torch.cat([s[o:o + n] for o, n in runs])
+            ops.append(dist.P2POp(dist.isend, buf, self._rank(dst), group=self.topo.pp_group))
+        for src, runs in sorted(plan.recv.items()):
+            buf = s.new_empty(1 if peer else sum(n for _, _, n in runs))
+            recv_bufs[src] = buf
+            ops.append(dist.P2POp(dist.irecv, buf, self._rank(src), group=self.topo.pp_group))
+        works = dist.batch_isend_irecv(ops) if ops else []
+        for t_off, s_off, n in plan.local:
+            self._blend(t[t_off:t_off + n], s[s_off:s_off + n], momentum)
+        for w in works:
+            w.wait()
+        for src, runs in sorted(plan.recv.items()):
+            pos = 0
+            for t_off, s_off, n in runs:
+                if peer:
+                    self._blend(t[t_off:t_off + n], self.peer_flats[src][s_off:s_off + n], momentum)
+                else:
+                    self._blend(t[t_off:t_off + n], recv_bufs[src][pos:pos + n], momentum)
+                pos += n
+
+    def _blend(self, t: torch.Tensor, s: torch.Tensor, momentum: float) -> None:
+        if self.use_kernel:
+            from ..ops import fused
+            fused.ema_update_(t, s, momentum)
+        else:
+            t.lerp_(s, 1.0 - momentum)
+
+
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class _Stored:
+    inputs: List[Any]                 # per nano: flat input leaves (leaf tensors requiring grad kept here)
+    outputs: List[Any]                # per nano: flat output leaves (with graph)
+    grad_in_idx: List[int]            # indices of input leaves that carry a gradient upstream
+    grad_out_idx: List[int]           # indices of output leaves that require grad
+
+
+class StageEngine:
+    def __init__(self, topo: Topology, config: Dict[str, Any], partition_online: nn.Module,
+                 partition_target: nn.Module, optimizer: Optional[torch.optim.Optimizer],
+                 loss_fn: Callable, target_update_fn: Optional[Callable], momentum: float,
+                 kd_mode: bool, target_train_mode: bool = True,
+                 scatter_gather_fn: ScatterGatherFn = defaultScatterGatherFn,
+                 args: Any = None, extra_args: Any = None, inbox=None, loss_sink: Optional[Callable] = None,
+                 profiler=None, ema_plan=None):
+        self.topo, self.cfg = topo, config
+        self.device = topo.device
+        self.cuda = topo.is_cuda
+        self.online, self.target = partition_online, partition_target
+        self.optimizer, self.loss_fn, self.momentum = optimizer, loss_fn, momentum
+        self.kd = kd_mode
+        self.sg = scatter_gather_fn
+        self.args, self.extra_args = args, extra_args
+        self.inbox = inbox if inbox is not None else queue.Queue()
+        self.loss_sink = loss_sink
+        self.profiler = profiler
+        rt = config["runtime"]
+        gp = config["gpipe_emulation"]
+        n_ub = gp["num_ubatch"] if gp["enabled"] else rt["num_ubatch"]
+        self.spec = ScheduleSpec(n_stages=topo.pp, n_ubatch=n_ub, bwd_split=rt["bwd_split"], kd=kd_mode,
+                                 skip_staleness=config["optimizer"]["num_skip_initial_staleness"],
+                                 gpipe=gp["enabled"])
+        self.U, self.S = self.spec.n_ubatch, self.spec.bwd_split
+        self.ga = max(int(config["optimizer"]["gradient_accumulation"]), 1)
+        self.skip_optimizer = bool(config["optimizer"]["skip_optimizer"])
+        self.autocast = rt["dtype"] == "bf16"
+        self.fused = bool(rt["fused"]) and self.cuda
+        self.channels_last = bool(rt["channels_last"])
+
+        self.online.to(self.device)
+        self.target.to(self.device)
+        if self.channels_last:
+            self.online.to(memory_format=torch.channels_last)
+            self.target.to(memory_format=torch.channels_last)
+        self.online.train()
+        self.target.train(target_train_mode)
+        for p in self.target.parameters():
+            p.requires_grad_(False)
+
+        # flat state ---------------------------------------------------------------------------
+        self.flat_online = FlatParams([p for p in self.online.parameters()], self.device, with_grad=True,
+                                      pad_to=max(topo.dp, 1))
+        self.flat_target = FlatParams([p for p in self.target.parameters()], self.device, with_grad=False)
+        self._bind_optimizer()
+        self.ema_plan = ema_plan
+        self.updater = self._make_updater(target_update_fn)
+
+        # streams / links ------------------------------------------------------------------------
+        if self.cuda:
+            self.compute = torch.cuda.Stream(self.device)
+            self.copy_stream = torch.cuda.Stream(self.device)
+            self.dp_stream = torch.cuda.Stream(self.device)
+        else:
+            self.compute = self.copy_stream = self.dp_stream = None
+        j = topo.stage
+        self.fwd_in = Link(topo.fwd_groups[j - 1], topo.prev_rank, self.device) if not topo.is_first else None
+        self.bwd_out = Link(topo.bwd_groups[j - 1], topo.prev_rank, self.device) if not topo.is_first else None
+        self.fwd_out = Link(topo.fwd_groups[j], topo.next_rank, self.device) if not topo.is_last else None
+        self.bwd_in = Link(topo.bwd_groups[j], topo.next_rank, self.device) if not topo.is_last else None
+        self.meta = MetaBoard(topo.store, topo.replica)
+
+        # run-time state -------------------------------------------------------------------------
+        self.feeds: Dict[int, FeedMsg] = {}
+        self.last_batch: Optional[int] = None
+        self.highest_fed = 0
+        self.acts: Dict[Tuple[int, int, int], _Stored] = {}            # (batch, view, ub) -> student activations
+        self.t_out: Dict[Tuple[int, int], List[Any]] = {}               # last stage: (batch, view) -> teacher outputs per ub
+        self.o_out: Dict[Tuple[int, int], List[Any]] = {}               # last stage: student outputs (flat leaves per nano)
+        self.out_grads: Dict[Tuple[int, int, int], List[torch.Tensor]] = {}   # last stage: (batch, view, nano) -> grads
+        self.fwd_posted: Dict[Tuple, RecvHandle] = {}
+        self.bwd_posted: Dict[Tuple, RecvHandle] = {}
+        self._fwd_iter = self._fwd_keys()
+        self._bwd_order: Dict[int, List[Op]] = {}
+        self._fwd_peek: Optional[Op] = None
+        self.ga_count = 0
+        self.force_steps: set = set()
+        self.steps_done = 0
+        self.error: Optional[BaseException] = None
+        self.thread: Optional[threading.Thread] = None
+        self.losses: "queue.Queue[Tuple[int, Any]]" = queue.Queue()
+        self._pending_loss: List[Tuple[int, torch.Tensor, Any]] = []
+        self.op_count = 0
+        self.on_batch_done: Optional[Callable[[int], None]] = None
+        self.on_idle: Optional[Callable[[], None]] = None
+        self._warm_links()
+
+    # -- set-up helpers ----------------------------------------------------------------------------
+    def _bind_optimizer(self) -> None:
+        """Optimizers from :mod:`tspipe_b200.optim` step the flat buffers in one or two launches."""
+        opt = self.optimizer
+        if opt is not None and hasattr(opt, "bind_flat"):
+            opt.bind_flat(self.flat_online, use_kernel=self.fused)
+
+    def _make_updater(self, fn: Optional[Callable]) -> TeacherUpdater:
+        if fn is None:
+            return FrozenTeacher()
+        if getattr(fn, "is_ema", False):
+            plan = self.ema_plan
+            if plan is None or plan.is_local_prefix:
+                if corresponding_prefix(self.flat_online, self.flat_target):
+                    return FlatEmaTeacher(self.flat_target, self.flat_online.data, use_kernel=self.fused)
+            else:
+                peers = None
+                if self.cuda and self.cfg["runtime"].get("peer_memory", True) and (plan.recv or plan.send):
+                    from ..comm import peer
+                    peers = peer.share_over_group(self.flat_online, self.topo)
+                return CrossStageEmaTeacher(self.topo, plan, self.flat_target, self.flat_online, peers,
+                                            use_kernel=self.fused)
+            fn = fn.reference_fn
+        n = len(self.flat_target.params)
+        return CallbackTeacher(fn, self.flat_online.params[:n], self.flat_target.params)
+
+    def _warm_links(self) -> None:
+        """Create every p2p communicator up front, boundary by boundary, in one global order."""
+        for j in range(self.topo.pp - 1):
+            for groups, down in ((self.topo.fwd_groups, True), (self.topo.bwd_groups, False)):
+                if j not in groups:
+                    continue
+                lo, hi = self.topo.rank_of(self.topo.replica, j), self.topo.rank_of(self.topo.replica, j + 1)
+                src, dst = (lo, hi) if down else (hi, lo)
+                t = torch.zeros(1, device=self.device)
+                if self.topo.rank == src:
+                    dist.send(t, dst, group=groups[j])
+                else:
+                    dist.recv(t, src, group=groups[j])
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+
+    # -- context managers --------------------------------------------------------------------------
+    def _on_compute(self):
+        return torch.cuda.stream(self.compute) if self.cuda else contextlib.nullcontext()
+
+    def _amp(self):
+        if self.autocast:
+            return torch.autocast(device_type=self.device.type, dtype=torch.bfloat16)
+        return contextlib.nullcontext()
+
+    def _prof(self, name: str, op: Op, is_target: bool = False):
+        if self.profiler is None:
+            return contextlib.nullcontext()
+        return self.profiler.operation(name, op.batch, op.view, op.ub, is_target, self.topo.stage)
+
+    # -- feeder side -------------------------------------------------------------------------------
+    def start(self) -> None:
+        self.thread = threading.Thread(target=self._run_guarded, name=f"tspipe-exec-{self.topo.rank}", daemon=True)
+        self.thread.start()
+
+    def join(self, timeout: Optional[float] = None) -> None:
+        if self.thread is not None:
+            self.thread.join(timeout)
+        if self.error is not None:
+            raise EngineError(f"stage engine on rank {self.topo.rank} failed") from self.error
+
+    def _run_guarded(self) -> None:
+        try:
+            self.run()
+        except BaseException as e:  # noqa: BLE001 - reported to the owner thread
+            self.error = e
+            Log.e(f"rank {self.topo.rank} executor died:\n{traceback.format_exc()}")
+            self.losses.put((-1, e))
+            try:
+                self.topo.store.set(f"dead/{self.topo.rank}", repr(e))
+            except Exception:
+                pass
+
+    # -- availability ------------------------------------------------------------------------------
+    def _pump(self, block: bool) -> bool:
+        try:
+            msg = self.inbox.get(timeout=0.2) if block else self.inbox.get_nowait()
+        except queue.Empty:
+            return False
+        if isinstance(msg, StopMsg):
+            self.last_batch = msg.last_batch
+        elif isinstance(msg, EpochMsg):
+            self.force_steps.add(msg.batch_id)
+        elif isinstance(msg, FeedMsg):
+            self.feeds[msg.batch_id] = msg
+            self.highest_fed = max(self.highest_fed, msg.batch_id)
+        else:
+            raise EngineError(f"unknown message {msg!r}")
+        return True
+
+    def _have_batch(self, b: int) -> bool:
+        """Block until batch ``b`` has been fed (True) or feeding stopped before it (False)."""
+        deadline = time.monotonic() + float(self.cfg["runtime"]["timeout_s"])
+        while True:
+            if b <= self.highest_fed:
+                return True
+            if self.last_batch is not None and b > self.last_batch:
+                return False
+            if not self._pump(block=True):
+                self._check_peers()
+                if time.monotonic() > deadline:
+                    raise EngineError(f"rank {self.topo.rank}: no batch {b} and no stop within the timeout")
+
+    def _check_peers(self) -> None:
+        if self.on_idle is not None:
+            self.on_idle()
+
+    # -- main loop ---------------------------------------------------------------------------------
+    def run(self) -> None:
+        b = 1
+        while self._have_batch(b):
+            for op in self._block_ops(b):
+                self._dispatch(op)
+            self._retire(b)
+            b += 1
+        self._drain()
+
+    def _block_ops(self, b: int):
+        """Yield the ops of batch block ``b``; resolves 'does batch b+1 exist' lazily, right before
+        the first look-ahead teacher forward."""
+        spec, j = self.spec, self.topo.stage
+        full = batch_block(spec, j, b, None)
+        decided: Optional[bool] = None
+        for op in full:
+            if op.kind == OpKind.T and op.batch == b + 1:
+                if decided is None:
+                    decided = self._have_batch(b + 1)
+                if not decided:
+                    continue
+            yield op
+
+    def _dispatch(self, op: Op) -> None:
+        self.op_count += 1
+        if op.kind == OpKind.T:
+            self._forward(op, teacher=True)
+        elif op.kind == OpKind.O:
+            self._forward(op, teacher=False)
+        elif op.kind == OpKind.B:
+            self._backward(op)
+        elif op.kind == OpKind.LOSS:
+            self._loss(op)
+        elif op.kind == OpKind.OPT:
+            self._optimize(op)
+
+    # -- input acquisition ---------------------------------------------------------------------------
+    def _net(self, teacher: bool) -> str:
+        return "t" if teacher else "o"
+
+    def _user_view(self, teacher: bool, view: int) -> int:
+        """Which fed view a (net, view) pair consumes.  SSL: schedule view v <-> ``view_{v+1}`` for both
+        nets; KD: teacher (view 1) takes ``view_2`` and the student (view 0) ``view_1``
+        (`gpu_task.py:548-575`)."""
+        return view
+
+    def _stage0_input(self, op: Op, teacher: bool) -> List[Any]:
+        msg = self.feeds[op.batch]
+        cache = getattr(msg, "_scattered", None)
+        if cache is None:
+            cache = {}
+            msg._scattered = cache
+        v = self._user_view(teacher, op.view)
+        if v not in cache:
+            cache[v] = self.sg.scatter(msg.views[v], self.U)
+        ub = cache[v][op.ub]
+        data = ub.value if isinstance(ub, Batch) else ub
+        if self.cuda:
+            if msg.ready_event is not None:
+                torch.cuda.current_stream().wait_event(msg.ready_event)
+            data = pt.tree_map_tensors(lambda t: t if t.is_cuda else self._h2d(t), data)
+        return data
+
+    def _h2d(self, t: torch.Tensor) -> torch.Tensor:
+        cur = torch.cuda.current_stream()
+        with torch.cuda.stream(self.copy_stream):
+            d = t.to(self.device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        cur.wait_event(ev)
+        d.record_stream(cur)
+        return d
+
+    def _recv_forward(self, op: Op, teacher: bool) -> Any:
+        """Upstream activation for ``op``: list (per nano-batch for the student, one for the teacher)
+        of stage-input pytrees.  Receives are posted in crossing order, ``prefetch`` items ahead."""
+        key = (op.kind, op.batch, op.view, op.ub)
+        while key not in self.fwd_posted:
+            nxt = self._next_fwd_key(blocking=True)
+            self._post_forward(nxt)
+        depth = int(self.cfg["runtime"].get("prefetch", 2))
+        while len(self.fwd_posted) <= depth:
+            nxt = self._next_fwd_key(blocking=False)
+            if nxt is None:
+                break
+            self._post_forward(nxt)
+        pieces = self.fwd_posted.pop(key)
+        return [_rebuild(h.wait(), others, tree, wrapped) for h, tree, wrapped, others in pieces]
+
+    def _fwd_keys(self):
+        b = 1
+        while True:
+            for o in batch_block(self.spec, self.topo.stage, b, None):
+                if o.kind in (OpKind.T, OpKind.O):
+                    yield o
+            b += 1
+
+    def _next_fwd_key(self, blocking: bool) -> Optional[Op]:
+        """Next forward item in crossing order.  Non-blocking mode returns None rather than wait for
+        an unknown batch or for an unpublished shape announcement."""
+        while True:
+            if self._fwd_peek is None:
+                self._fwd_peek = next(self._fwd_iter)
+            o = self._fwd_peek
+            if self.last_batch is not None and o.batch > self.last_batch:
+                # never fed: it will not cross the link.  Items of batch last+1 are look-ahead teacher
+                # forwards interleaved with real items of batch `last`; anything later ends the stream.
+                if o.batch > self.last_batch + 1:
+                    if blocking:
+                        raise EngineError("forward item requested beyond the last fed batch")
+                    return None
+                self._fwd_peek = None
+                continue
+            if o.batch > self.highest_fed:
+                if not blocking:
+                    self._pump(block=False)
+                    if o.batch > self.highest_fed:
+                        return None
+                elif not self._have_batch(o.batch):
+                    self._fwd_peek = None
+                    continue
+            if not blocking:
+                epoch = self.feeds[o.batch].shape_epoch
+                if not self.meta.cached(f"f{self.topo.stage - 1}", self._net(o.kind == OpKind.T), epoch):
+                    return None
+            self._fwd_peek = None
+            return o
+
+    def _post_forward(self, o: Op) -> None:
+        net = self._net(o.kind == OpKind.T)
+        epoch = self.feeds[o.batch].shape_epoch
+        meta = self.meta.fetch(f"f{self.topo.stage - 1}", net, epoch)
+        self.fwd_posted[(o.kind, o.batch, o.view, o.ub)] = [
+            (self.fwd_in.post_recv(specs), tree, wrapped, others) for specs, tree, wrapped, others in meta]
+
+    # -- forward -------------------------------------------------------------------------------------
+    def _forward(self, op: Op, teacher: bool) -> None:
+        first, last = self.topo.is_first, self.topo.is_last
+        module = self.target if teacher else self.online
+        n_piece = 1 if teacher else self.S
+        with self._on_compute(), self._prof("compute", op, teacher):
+            if first:
+                data = self._stage0_input(op, teacher)
+                pieces = [data] if n_piece == 1 else pt.generic_scatter(data, n_piece)
+            else:
+                pieces = self._recv_forward(op, teacher)
+            outs, stored_in, stored_out = [], [], []
+            gin_idx: List[int] = []
+            gout_idx: List[int] = []
+            for x in pieces:
+                leaves, tree, wrapped = pt.flatten(x)
+                if not teacher and not first:
+                    gin_idx = [i for i, l in enumerate(leaves) if isinstance(l, torch.Tensor) and l.is_floating_point()]
+                    for i in gin_idx:
+                        leaves[i] = leaves[i].detach().requires_grad_(True)
+                    x = pt.unflatten(leaves, tree, wrapped)
+                if self.channels_last:
+                    x = pt.tree_map_tensors(_to_channels_last, x)
+                if teacher:
+                    with torch.no_grad(), self._amp():
+                        y = module(x)
+                else:
+                    with self._amp():
+                        y = module(x)
+                outs.append(y)
+                if not teacher:
+                    oleaves = pt.flatten(y)[0]
+                    gout_idx = [i for i, l in enumerate(oleaves)
+                                if isinstance(l, torch.Tensor) and l.requires_grad and l.dim() > 0]
+                    stored_in.append(leaves)
+                    stored_out.append(oleaves)
+            if not teacher:
+                self.acts[(op.batch, op.view, op.ub)] = _Stored(stored_in, stored_out, gin_idx, gout_idx)
+            if not last:
+                self._send_forward(op, teacher, outs)
+            else:
+                key = (op.batch, op.view)
+                if teacher:
+                    self.t_out.setdefault(key, [None] * self.U)[op.ub] = outs[0]
+                else:
+                    self.o_out.setdefault(key, [None] * self.U)[op.ub] = outs
+
+    def _send_forward(self, op: Op, teacher: bool, outs: List[Any]) -> None:
+        net = self._net(teacher)
+        epoch = self.feeds[op.batch].shape_epoch
+        meta, tensors = [], []
+        for y in outs:
+            leaves, tree, wrapped = pt.flatten(y)
+            ts = [l.detach() for l in leaves if isinstance(l, torch.Tensor)]
+            others = [(i, l) for i, l in enumerate(leaves) if not isinstance(l, torch.Tensor)]
+            meta.append(([(tuple(t.shape), t.dtype) for t in ts], tree, wrapped, others))
+            tensors.append(ts)
+        self.meta.publish(f"f{self.topo.stage}", net, epoch, meta)
+        for ts in tensors:
+            self.fwd_out.send(ts)
+
+    # -- loss ----------------------------------------------------------------------------------------
+    def _loss(self, op: Op) -> None:
+        b = op.batch
+        msg = self.feeds[b]
+        with self._on_compute(), self._prof("loss", op):
+            online_full, leaf_sets = [], []
+            for v in self.spec.student_views:
+                nano_outs = [y for ub in self.o_out.pop((b, v)) for y in ub]          # U*S stage outputs
+                flat = [pt.flatten(y) for y in nano_outs]
+                tree, wrapped = flat[0][1], flat[0][2]
+                cat_leaves = []
+                for i, l in enumerate(flat[0][0]):
+                    if isinstance(l, torch.Tensor) and l.dim() > 0:
+                        t = torch.cat([f[0][i].detach() for f in flat]) if len(flat) > 1 else l.detach()
+                        if l.requires_grad:
+                            t.requires_grad_(True)
+                        cat_leaves.append(t)
+                    else:
+                        cat_leaves.append(l.detach() if isinstance(l, torch.Tensor) else l)
+                leaf_sets.append((v, cat_leaves, [f[0] for f in flat]))
+                online_full.append(pt.unwrap(pt.unflatten(cat_leaves, tree, wrapped)))
+            target_full = []
+            for v in self.spec.teacher_views:
+                outs = self.t_out.pop((b, v))
+                target_full.append(pt.unwrap(self.sg.gather([Batch(pt.unwrap(o)) for o in outs])))
+            with self._amp():
+                if self.kd:
+                    labels = msg.labels
+                    if self.cuda and labels is not None:
+                        labels = pt.tree_map_tensors(lambda t: t if t.is_cuda else self._h2d(t), labels)
+                    loss = self.loss_fn(online_full[0], target_full[0], labels, self.args, self.extra_args, msg.epoch)
+                else:
+                    loss = self.loss_fn(online_full[0], online_full[1], target_full[0], target_full[1],
+                                        self.args, self.extra_args)
+            self._report_loss(b, loss.detach())
+            torch.autograd.backward(loss)
+            n_nano = self.U * self.S
+            for v, cat_leaves, per_nano in leaf_sets:
+                grads_per_nano: List[List[torch.Tensor]] = [[] for _ in range(n_nano)]
+                for i, t in enumerate(cat_leaves):
+                    if isinstance(t, torch.Tensor) and t.requires_grad:
+                        g = t.grad if t.grad is not None else torch.zeros_like(t)
+                        sizes = [leaves[i].shape[0] for leaves in per_nano]
+                        for k, gk in enumerate(g.split(sizes)):
+                            grads_per_nano[k].append(gk)
+                for k in range(n_nano):
+                    self.out_grads[(b, v, k)] = grads_per_nano[k]
+
+    def _report_loss(self, b: int, loss: torch.Tensor) -> None:
+        if self.cuda:
+            host = torch.empty((), dtype=torch.float32, pin_memory=True)
+            host.copy_(loss.float(), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self.losses.put((b, (host, ev)))
+        else:
+            self.losses.put((b, float(loss)))
+
+    # -- backward ------------------------------------------------------------------------------------
+    def _backward(self, op: Op) -> None:
+        b, v, k = op.batch, op.view, op.ub
+        ub, piece = divmod(k, self.S)
+        st = self.acts[(b, v, ub)]
+        with self._on_compute(), self._prof("backward", op):
+            outs = [st.outputs[piece][i] for i in st.grad_out_idx]
+            if self.topo.is_last:
+                grads = self.out_grads.pop((b, v, k))
+            else:
+                grads = self._recv_backward(op)
+            if outs:
+                torch.autograd.backward(outs, grads)
+            if not self.topo.is_first:
+                gin = []
+                for i in st.grad_in_idx:
+                    leaf = st.inputs[piece][i]
+                    gin.append(leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
+                self.bwd_out.send(gin)
+            st.outputs[piece] = None
+            st.inputs[piece] = None
+            if all(o is None for o in st.outputs):
+                del self.acts[(b, v, ub)]
+
+    def _recv_backward(self, op: Op) -> List[torch.Tensor]:
+        """Gradient of one nano-batch from downstream; receives for the next ``prefetch`` backward items
+        of the batch are posted too (their shapes are those of the stored stage outputs)."""
+        order = self._bwd_order.get(op.batch)
+        if order is None:
+            order = self.spec.backward_items(op.batch, self.topo.stage)
+            self._bwd_order = {op.batch: order}
+        i = next(n for n, o in enumerate(order) if o.view == op.view and o.ub == op.ub)
+        depth = int(self.cfg["runtime"].get("prefetch", 2))
+        for o in order[i: i + 1 + depth]:
+            key = (o.batch, o.view, o.ub)
+            if key in self.bwd_posted:
+                continue
+            ub, piece = divmod(o.ub, self.S)
+            st = self.acts[(o.batch, o.view, ub)]
+            specs = [(tuple(st.outputs[piece][n].shape), st.outputs[piece][n].dtype) for n in st.grad_out_idx]
+            self.bwd_posted[key] = self.bwd_in.post_recv(specs)
+        return self.bwd_posted.pop((op.batch, op.view, op.ub)).wait()
+
+    # -- optimize ------------------------------------------------------------------------------------
+    def _optimize(self, op: Op) -> None:
+        b = op.batch
+        msg = self.feeds[b]
+        if msg.new_momentum is not None:
+            self.momentum = msg.new_momentum
+        if msg.new_lr is not None and self.optimizer is not None:
+            lrs = msg.new_lr if isinstance(msg.new_lr, (list, tuple)) else [msg.new_lr] * len(self.optimizer.param_groups)
+            for g, lr in zip(self.optimizer.param_groups, lrs):
+                g["lr"] = lr
+        if self.ga > 1:
+            self._have_batch(b + 1)        # an epoch-boundary notice for b precedes the next feed / stop
+        force = msg.force_step or b in self.force_steps
+        skip = self.skip_optimizer or ((self.ga_count + 1) % self.ga != 0 and not force)
+        with self._on_compute(), self._prof("optimize", op):
+            if skip:
+                if self.ga > 1 and not self.skip_optimizer:
+                    self.ga_count += 1
+                else:
+                    self.flat_online.zero_grad()
+                return
+            self.flat_online.collect_stray_grads()
+            if self.ga > 1:
+                self.flat_online.grad.div_(self.ga_count + 1)
+                self.ga_count = 0
+            self._dp_sync()
+            if self.optimizer is not None:
+                self.optimizer.step()
+            self.updater.step(self.momentum)
+            self.flat_online.zero_grad()
+            self.steps_done += 1
+
+    def _dp_sync(self) -> None:
+        if self.topo.dp_group is None:
+            return
+        opt = self.optimizer
+        if opt is not None and getattr(opt, "handles_dp", False):
+            return          # the fused reduce-scatter + step path does its own synchronisation
+        dist.all_reduce(self.flat_online.grad, op=dist.ReduceOp.SUM, group=self.topo.dp_group)
+        self.flat_online.grad.div_(self.topo.dp)
+
+    # -- retire / drain ------------------------------------------------------------------------------
+    def _retire(self, b: int) -> None:
+        self.feeds.pop(b - 1, None)
+        if self.on_batch_done is not None:
+            self.on_batch_done(b)
+
+    def _drain(self) -> None:
+        for link in (self.fwd_out, self.bwd_out):
+            if link is not None:
+                link.flush()
+        if self.cuda:
+            self.compute.synchronize()
+
+
+def _to_channels_last(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous(memory_format=torch.channels_last) if t.dim() == 4 else t
+
+
+def _rebuild(tensors: List[torch.Tensor], others: List[Tuple[int, Any]], tree: Any, wrapped: bool) -> Any:
+    n = len(tensors) + len(others)
+    leaves: List[Any] = [None] * n
+    taken = set()
+    for i, l in others:
+        leaves[i] = l
+        taken.add(i)
+    it = iter(tensors)
+    for i in range(n):
+        if i not in taken:
+            leaves[i] = next(it)
+    return pt.unflatten(leaves, tree, wrapped)
