@@ -1,0 +1,269 @@
+// LayerNorm forward/backward, GELU forward/backward, and microbatch BatchNorm (channels-last) kernels, sm_100a.
+//
+// Reference call sites: ViT / BERT blocks (`benchmarks/moco-v3/vits.py:132`, `benchmarks/distilbert/bert.py`),
+// GELU inside their MLPs, and the microbatch-aware BatchNorm (`tspipe/batchnorm.py:45-120`), all plain ATen calls
+// there.  Under bf16 autocast ATen's layer_norm up-casts to fp32 and writes fp32; these kernels read and write
+// the activation dtype directly and keep statistics in fp32.
+#include "common.cuh"
+#include "tspipe_kernels.h"
+
+namespace {
+
+constexpr int kLnMaxVec = 4;   // per-lane register tile: 4 x 8 elements -> rows up to 1024 wide stay in registers
+
+// ---------------------------------------------------------------------------------------------
+// LayerNorm forward: one warp per row.  D % 8 == 0 and D <= 1024 -> single pass from registers.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) ln_fwd_kernel(const T* __restrict__ x, const float* __restrict__ w,
+                                                     const float* __restrict__ b, T* __restrict__ y,
+                                                     float* __restrict__ mean, float* __restrict__ rstd, int rows,
+                                                     int d, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= rows) return;
+  const T* xr = x + (int64_t)row * d;
+  T* yr = y + (int64_t)row * d;
+  float v[kLnMaxVec][8];
+  float s = 0.f;
+  const int nvec = d >> 3;
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+      tsp::ld8(xr, (int64_t)vi * 8, v[k]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += v[k][e];
+    }
+  }
+  const float mu = tsp::warp_sum(s) / d;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { const float c = v[k][e] - mu; q += c * c; }
+    }
+  }
+  const float rs = rsqrtf(tsp::warp_sum(q) / d + eps);
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+      float wv[8], bv[8], o[8];
+      tsp::ld8(w, (int64_t)vi * 8, wv);
+      tsp::ld8(b, (int64_t)vi * 8, bv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[k][e] - mu) * rs * wv[e] + bv[e];
+      tsp::st8(yr, (int64_t)vi * 8, o);
+    }
+  }
+}
+
+// LayerNorm backward, part 1: dx per row (one warp per row) + per-block partial dw/db over the block's rows.
+// partial layout: [gridDim.x][2][d] fp32 (scratch memory owned by the caller).
+template <typename T>
+__global__ void __launch_bounds__(128) ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                     const float* __restrict__ w, const float* __restrict__ mean,
+                                                     const float* __restrict__ rstd, T* __restrict__ dx,
+                                                     float* __restrict__ partial, int rows, int d,
+                                                     int rows_per_block) {
+  extern __shared__ float sm[];            // [2][d] accumulators for the block
+  float* sdw = sm;
+  float* sdb = sm + d;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) sm[i] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = d >> 3;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  float adw[kLnMaxVec][8], adb[kLnMaxVec][8];
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { adw[k][e] = 0.f; adb[k][e] = 0.f; }
+  for (int row = row0 + warp; row < row1; row += 4) {
+    const T* xr = x + (int64_t)row * d;
+    const T* gr = dy + (int64_t)row * d;
+    T* dr = dx + (int64_t)row * d;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[kLnMaxVec][8], gw[kLnMaxVec][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnMaxVec; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float xv[8], gv[8], wv[8];
+        tsp::ld8(xr, (int64_t)vi * 8, xv);
+        tsp::ld8(gr, (int64_t)vi * 8, gv);
+        tsp::ld8(w, (int64_t)vi * 8, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[k][e] = (xv[e] - mu) * rs;
+          gw[k][e] = gv[e] * wv[e];
+          s1 += gw[k][e];
+          s2 += gw[k][e] * xh[k][e];
+          adw[k][e] += gv[e] * xh[k][e];
+          adb[k][e] += gv[e];
+        }
+      }
+    }
+    s1 = tsp::warp_sum(s1) / d;
+    s2 = tsp::warp_sum(s2) / d;
+#pragma unroll
+    for (int k = 0; k < kLnMaxVec; ++k) {
+      const int vi = lane + 32 * k;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rs * (gw[k][e] - s1 - xh[k][e] * s2);
+        tsp::st8(dr, (int64_t)vi * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        atomicAdd(sdw + vi * 8 + e, adw[k][e]);
+        atomicAdd(sdb + vi * 8 + e, adb[k][e]);
+      }
+    }
+  }
+  __syncthreads();
+  float* out = partial + (int64_t)blockIdx.x * 2 * d;
+  for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) out[i] = sm[i];
+}
+
+// part 2: dw[j] = sum_blocks partial[b][0][j], db likewise.
+__global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ partial, int nblocks, int d,
+                                                            float* __restrict__ dw, float* __restrict__ db) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= 2 * d) return;
+  float acc = 0.f;
+  for (int b = 0; b < nblocks; ++b) acc += partial[(int64_t)b * 2 * d + j];
+  if (j < d) dw[j] = acc; else db[j - d] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// GELU (erf form), optionally with the bias add in front: y = gelu(x + bias)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_grad_f(float x) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ x, const float* __restrict__ bias,
+                                                       T* __restrict__ y, int64_t n, int d) {
+  const int64_t nv = n >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8], o[8];
+    tsp::ld8(x, i * 8, v);
+    if (bias) {
+      float b[8];
+      tsp::ld8(bias, (i * 8) % d, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += b[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = gelu_f(v[e]);
+    tsp::st8(y, i * 8, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                       const float* __restrict__ bias, T* __restrict__ dx, int64_t n,
+                                                       int d) {
+  const int64_t nv = n >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
+    float v[8], g[8], o[8];
+    tsp::ld8(x, i * 8, v);
+    tsp::ld8(dy, i * 8, g);
+    if (bias) {
+      float b[8];
+      tsp::ld8(bias, (i * 8) % d, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += b[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = g[e] * gelu_grad_f(v[e]);
+    tsp::st8(dx, i * 8, o);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int tsp_layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int rows, int d,
+                      float eps, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 8 != 0 || d > 8 * 32 * kLnMaxVec) return -3;
+  const int grid = (rows + 3) / 4;
+  if (dtype == TSP_DTYPE_BF16)
+    ln_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, w, b, (__nv_bfloat16*)y, mean, rstd,
+                                                           rows, d, eps);
+  else
+    ln_fwd_kernel<float><<<grid, 128, 0, stream>>>((const float*)x, w, b, (float*)y, mean, rstd, rows, d, eps);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_layernorm_bwd_blocks(int rows) {
+  int nb = (rows + 63) / 64;
+  const int cap = 148 * 4;
+  return nb > cap ? cap : (nb < 1 ? 1 : nb);
+}
+
+// `partial` is scratch of tsp_layernorm_bwd_blocks(rows) * 2 * d floats.
+int tsp_layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                      float* dw, float* db, float* partial, int rows, int d, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 8 != 0 || d > 8 * 32 * kLnMaxVec) return -3;
+  const int nb = tsp_layernorm_bwd_blocks(rows);
+  const int rpb = (rows + nb - 1) / nb;
+  const size_t smem = sizeof(float) * 2 * (size_t)d;
+  if (dtype == TSP_DTYPE_BF16)
+    ln_bwd_kernel<__nv_bfloat16><<<nb, 128, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, mean,
+                                                            rstd, (__nv_bfloat16*)dx, partial, rows, d, rpb);
+  else
+    ln_bwd_kernel<float><<<nb, 128, smem, stream>>>((const float*)dy, (const float*)x, w, mean, rstd, (float*)dx,
+                                                    partial, rows, d, rpb);
+  ln_bwd_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, stream>>>(partial, nb, d, dw, db);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_gelu_fwd(const void* x, const float* bias, void* y, int64_t n, int d, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || (bias && d % 8 != 0)) return -3;
+  int64_t blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == TSP_DTYPE_BF16)
+    gelu_fwd_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, bias, (__nv_bfloat16*)y, n, d);
+  else
+    gelu_fwd_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)x, bias, (float*)y, n, d);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int64_t n, int d, int dtype,
+                 cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || (bias && d % 8 != 0)) return -3;
+  int64_t blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == TSP_DTYPE_BF16)
+    gelu_bwd_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, bias,
+                                                                    (__nv_bfloat16*)dx, n, d);
+  else
+    gelu_bwd_kernel<float><<<(int)blocks, 256, 0, stream>>>((const float*)dy, (const float*)x, bias, (float*)dx, n, d);
+  return TSP_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -1,0 +1,50 @@
+// C entry points of libtspipe_b200.so (all kernels are compiled for sm_100a only).
+// Every function enqueues on `stream` and returns 0 on success, a cudaError_t value, or a negative
+// code for rejected arguments (-2 misaligned pointer, -3 unsupported shape).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- flat_optim.cu ---------------------------------------------------------------------------------------------
+int tsp_ema_update(float* teacher, const float* student, int64_t n, float momentum, void* bf16_shadow,
+                   cudaStream_t stream);
+int tsp_lars_step(float* p, const float* g, float* mu, const int64_t* chunks, int n_chunks, const float* seg_hp,
+                  float grad_scale, float* norms, int n_seg, float* teacher, int64_t teacher_n, float ema_m,
+                  cudaStream_t stream);
+int tsp_lars_norms(const float* p, const float* g, const int64_t* chunks, int n_chunks, const float* seg_hp,
+                   float grad_scale, float* norms, int n_seg, cudaStream_t stream);
+int tsp_lars_apply(float* p, const float* g, float* mu, const int64_t* chunks, int n_chunks, const float* seg_hp,
+                   float grad_scale, const float* norms, float* teacher, int64_t teacher_n, float ema_m,
+                   cudaStream_t stream);
+int tsp_adamw_step(float* p, const float* g, float* m, float* v, const int64_t* chunks, int n_chunks,
+                   const float* seg_hp, float grad_scale, float* teacher, int64_t teacher_n, float ema_m,
+                   cudaStream_t stream);
+int tsp_sgd_step(float* p, const float* g, float* buf, const int64_t* chunks, int n_chunks, const float* seg_hp,
+                 float grad_scale, float* teacher, int64_t teacher_n, float ema_m, cudaStream_t stream);
+
+// ---- losses.cu ---------------------------------------------------------------------------------------------------
+int tsp_byol_loss(const void* x, const void* y, int n, int d, int dtype, float scale, float* loss, void* gx,
+                  cudaStream_t stream);
+int tsp_cosine_loss(const void* x, const void* y, const uint8_t* row_mask, int n, int d, int dtype, float scale,
+                    float* loss, void* gx, cudaStream_t stream);
+int tsp_kd_ce_loss(const void* s, const void* t, const int64_t* labels, const uint8_t* row_mask, int n, int c,
+                   int s_dtype, int t_dtype, float temp, float w_ce, float w_kd, float* loss, void* gs,
+                   cudaStream_t stream);
+
+// ---- norms.cu ----------------------------------------------------------------------------------------------------
+int tsp_layernorm_fwd(const void* x, const float* w, const float* b, void* y, float* mean, float* rstd, int rows, int d,
+                      float eps, int dtype, cudaStream_t stream);
+int tsp_layernorm_bwd_blocks(int rows);
+int tsp_layernorm_bwd(const void* dy, const void* x, const float* w, const float* mean, const float* rstd, void* dx,
+                      float* dw, float* db, float* partial, int rows, int d, int dtype, cudaStream_t stream);
+int tsp_gelu_fwd(const void* x, const float* bias, void* y, int64_t n, int d, int dtype, cudaStream_t stream);
+int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int64_t n, int d, int dtype,
+                 cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -83,37 +83,54 @@ class Link:
 
 
 class MetaBoard:
-    """Shape/structure announcements through the rendezvous store.
+    """Structure / shape announcements through the rendezvous store.
 
-    A sender publishes the pytree structure and tensor specs of what crosses a link the
-    first time it sends for a given ``(link, net, shape_epoch)``; the receiver blocks on the
-    key only then.  (The reference ships this metadata with every message by RPC,
-    `tspipe/communicator.py:84-99,251-267`.)"""
+    For every ``(link, net, batch)`` the sender publishes once the pytree structure and tensor specs
+    of what crosses the link (identical for all microbatches of the batch); the receiver reads the key
+    before posting the batch's first receive and deletes it.  The reference ships this metadata with
+    every single message by RPC (`tspipe/communicator.py:84-99,251-267`)."""
 
     def __init__(self, store, replica: int):
         self.store, self.replica = store, replica
         self._sent: Dict[str, bytes] = {}
         self._got: Dict[str, Any] = {}
 
-    def _key(self, link: str, net: str, epoch: int) -> str:
-        return f"meta/{self.replica}/{link}/{net}/{epoch}"
+    def _key(self, link: str, net: str, batch: int) -> str:
+        return f"meta/{self.replica}/{link}/{net}/{batch}"
 
-    def publish(self, link: str, net: str, epoch: int, meta: Any) -> None:
-        key = self._key(link, net, epoch)
+    def publish(self, link: str, net: str, batch: int, meta: Any) -> None:
+        key = self._key(link, net, batch)
         blob = pickle.dumps(meta)
         prev = self._sent.get(key)
         if prev is None:
             self.store.set(key, blob)
             self._sent[key] = blob
+            for k in [k for k in self._sent if k.endswith(f"/{batch - 4}")]:
+                del self._sent[k]
         elif prev != blob:
-            raise RuntimeError(f"stage output structure changed within shape epoch {epoch} on {link}/{net}; "
-                               "feed batches of a different shape through a new shape epoch")
+            raise RuntimeError(f"stage output structure differs between microbatches of batch {batch} on "
+                               f"{link}/{net}: all microbatches of a batch must have the same shapes")
 
-    def cached(self, link: str, net: str, epoch: int) -> bool:
-        return self._key(link, net, epoch) in self._got
+    def cached(self, link: str, net: str, batch: int) -> bool:
+        key = self._key(link, net, batch)
+        if key in self._got:
+            return True
+        try:
+            if not self.store.check([key]):
+                return False
+        except Exception:
+            return False
+        self.fetch(link, net, batch)
+        return True
 
-    def fetch(self, link: str, net: str, epoch: int) -> Any:
-        key = self._key(link, net, epoch)
+    def fetch(self, link: str, net: str, batch: int) -> Any:
+        key = self._key(link, net, batch)
         if key not in self._got:
             self._got[key] = pickle.loads(self.store.get(key))
+            try:
+                self.store.delete_key(key)
+            except Exception:
+                pass
+            for k in [k for k in self._got if k.endswith(f"/{batch - 4}")]:
+                del self._got[k]
         return self._got[key]

@@ -1,0 +1,1 @@
+"""Hand-written sm_100a kernels and their autograd wrappers."""

@@ -51,7 +51,6 @@ class FeedMsg:
     batch_id: int
     views: Optional[List[Any]] = None          # [view_1, view_2] mini-batch data (stage 0 only)
     labels: Any = None                         # last stage only (KD mode)
-    shape_epoch: int = 0
     new_lr: Any = None                         # scalar or per-group list, applied at OPT(batch_id)
     new_momentum: Optional[float] = None
     force_step: bool = False                   # epoch boundary: step even if accumulation is incomplete
@@ -61,6 +60,13 @@ class FeedMsg:
 
 @dataclass
 class StopMsg:
+    last_batch: int
+
+
+@dataclass
+class FlushMsg:
+    """Finish every batch up to ``last_batch`` without look-ahead, then wait for more feeds; the next
+    batch refills the pipeline."""
     last_batch: int
 
 
@@ -116,6 +122,22 @@ class FlatEmaTeacher(TeacherUpdater):
             fused.ema_update_(self.teacher.data, self.student_flat[:n], momentum)
         else:
             self.teacher.data.lerp_(self.student_flat[:n], 1.0 - momentum)
+
+
+class OptimizerFusedEma(TeacherUpdater):
+    """The momentum update rides in the optimizer's own launch (:mod:`tspipe_b200.optim.flat`):
+    the freshly written student value is blended into the local teacher buffer before it leaves
+    the registers, so the step touches the teacher once and the student not at all again."""
+
+    def __init__(self, optimizer, teacher: FlatParams):
+        self.optimizer = optimizer
+        optimizer.teacher_flat = teacher.data
+
+    def before_step(self, momentum: float) -> None:
+        self.optimizer.ema_momentum = momentum
+
+    def step(self, momentum: float) -> None:
+        return
 
 
 class CrossStageEmaTeacher(TeacherUpdater):
@@ -259,6 +281,9 @@ class StageEngine:
         self._fwd_peek: Optional[Op] = None
         self.ga_count = 0
         self.force_steps: set = set()
+        self.fill_batches: set = {self.spec.skip_staleness + 1}
+        self._flushing = False
+        self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
         self.error: Optional[BaseException] = None
         self.thread: Optional[threading.Thread] = None
@@ -283,6 +308,8 @@ class StageEngine:
             plan = self.ema_plan
             if plan is None or plan.is_local_prefix:
                 if corresponding_prefix(self.flat_online, self.flat_target):
+                    if hasattr(self.optimizer, "bind_flat") and self.cfg["runtime"].get("fuse_ema", True):
+                        return OptimizerFusedEma(self.optimizer, self.flat_target)
                     return FlatEmaTeacher(self.flat_target, self.flat_online.data, use_kernel=self.fused)
             else:
                 peers = None
@@ -356,6 +383,10 @@ class StageEngine:
             return False
         if isinstance(msg, StopMsg):
             self.last_batch = msg.last_batch
+            self._flushing = False
+        elif isinstance(msg, FlushMsg):
+            self.last_batch = msg.last_batch
+            self._flushing = True
         elif isinstance(msg, EpochMsg):
             self.force_steps.add(msg.batch_id)
         elif isinstance(msg, FeedMsg):
@@ -385,18 +416,32 @@ class StageEngine:
     # -- main loop ---------------------------------------------------------------------------------
     def run(self) -> None:
         b = 1
-        while self._have_batch(b):
+        while True:
+            if not self._have_batch(b):
+                self._drain()
+                if not self._flushing:
+                    return
+                # flushed: resume with batch b as a pipeline-fill batch
+                self._flushing = False
+                self.last_batch = None
+                self.fill_batches.add(b)
+                self._fwd_iter, self._fwd_peek = self._fwd_keys(b), None
+                if self.on_flushed is not None:
+                    self.on_flushed(b - 1)
+                continue
             for op in self._block_ops(b):
                 self._dispatch(op)
             self._retire(b)
             b += 1
-        self._drain()
+
+    def _is_fill(self, b: int) -> bool:
+        return b in self.fill_batches
 
     def _block_ops(self, b: int):
         """Yield the ops of batch block ``b``; resolves 'does batch b+1 exist' lazily, right before
         the first look-ahead teacher forward."""
         spec, j = self.spec, self.topo.stage
-        full = batch_block(spec, j, b, None)
+        full = batch_block(spec, j, b, None, fill=self._is_fill(b))
         decided: Optional[bool] = None
         for op in full:
             if op.kind == OpKind.T and op.batch == b + 1:
@@ -472,10 +517,10 @@ class StageEngine:
         pieces = self.fwd_posted.pop(key)
         return [_rebuild(h.wait(), others, tree, wrapped) for h, tree, wrapped, others in pieces]
 
-    def _fwd_keys(self):
-        b = 1
+    def _fwd_keys(self, start: int = 1):
+        b = start
         while True:
-            for o in batch_block(self.spec, self.topo.stage, b, None):
+            for o in batch_block(self.spec, self.topo.stage, b, None, fill=self._is_fill(b)):
                 if o.kind in (OpKind.T, OpKind.O):
                     yield o
             b += 1
@@ -505,16 +550,14 @@ class StageEngine:
                     self._fwd_peek = None
                     continue
             if not blocking:
-                epoch = self.feeds[o.batch].shape_epoch
-                if not self.meta.cached(f"f{self.topo.stage - 1}", self._net(o.kind == OpKind.T), epoch):
+                if not self.meta.cached(f"f{self.topo.stage - 1}", self._net(o.kind == OpKind.T), o.batch):
                     return None
             self._fwd_peek = None
             return o
 
     def _post_forward(self, o: Op) -> None:
         net = self._net(o.kind == OpKind.T)
-        epoch = self.feeds[o.batch].shape_epoch
-        meta = self.meta.fetch(f"f{self.topo.stage - 1}", net, epoch)
+        meta = self.meta.fetch(f"f{self.topo.stage - 1}", net, o.batch)
         self.fwd_posted[(o.kind, o.batch, o.view, o.ub)] = [
             (self.fwd_in.post_recv(specs), tree, wrapped, others) for specs, tree, wrapped, others in meta]
 
@@ -567,7 +610,6 @@ class StageEngine:
 
     def _send_forward(self, op: Op, teacher: bool, outs: List[Any]) -> None:
         net = self._net(teacher)
-        epoch = self.feeds[op.batch].shape_epoch
         meta, tensors = [], []
         for y in outs:
             leaves, tree, wrapped = pt.flatten(y)
@@ -575,7 +617,7 @@ class StageEngine:
             others = [(i, l) for i, l in enumerate(leaves) if not isinstance(l, torch.Tensor)]
             meta.append(([(tuple(t.shape), t.dtype) for t in ts], tree, wrapped, others))
             tensors.append(ts)
-        self.meta.publish(f"f{self.topo.stage}", net, epoch, meta)
+        self.meta.publish(f"f{self.topo.stage}", net, op.batch, meta)
         for ts in tensors:
             self.fwd_out.send(ts)
 
@@ -706,6 +748,8 @@ class StageEngine:
                 self.flat_online.grad.div_(self.ga_count + 1)
                 self.ga_count = 0
             self._dp_sync()
+            if hasattr(self.updater, "before_step"):
+                self.updater.before_step(self.momentum)
             if self.optimizer is not None:
                 self.optimizer.step()
             self.updater.step(self.momentum)

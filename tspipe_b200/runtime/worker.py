@@ -67,6 +67,7 @@ def _worker_main(global_rank: int, world: int, pp: int, dp: int, cfg: Dict[str, 
                 from ..ckpt import save_partition
                 save_partition(art, b, topo.stage, engine, replica=topo.replica)
         engine.on_batch_done = on_done
+        engine.on_flushed = lambda b: outbox.put(("flushed", global_rank, b))
 
         stop_fwd = threading.Event()
 
@@ -167,6 +168,7 @@ class SpawnedPipeline:
         self.losses: "queue.Queue" = queue.Queue()
         self.done: Dict[int, int] = defaultdict(int)
         self.finals: Dict[int, Any] = {}
+        self.flushed: Dict[int, int] = {}
         self.final_online_state: Dict[int, Any] = {}
         self.final_target_state: Dict[int, Any] = {}
         self._losses_returned = 0
@@ -198,6 +200,8 @@ class SpawnedPipeline:
                 self.done[ev[1]] = ev[2]
             elif kind == "final":
                 self.finals[ev[1]] = ev[2]
+            elif kind == "flushed":
+                self.flushed[ev[1]] = ev[2]
             return ev
 
     def _drain_events(self) -> None:
@@ -214,6 +218,8 @@ class SpawnedPipeline:
                 self.done[ev[1]] = ev[2]
             elif ev[0] == "final":
                 self.finals[ev[1]] = ev[2]
+            elif ev[0] == "flushed":
+                self.flushed[ev[1]] = ev[2]
 
     # -- feeding --------------------------------------------------------------------------------------
     def submit(self, msg, views: List[Any], labels: Any) -> None:
@@ -252,6 +258,19 @@ class SpawnedPipeline:
                 if not block:
                     return None
                 self._next_event(timeout=self._timeout)
+
+    def flush(self, last_batch: int) -> List[float]:
+        from .engine import FlushMsg
+        self.broadcast(FlushMsg(last_batch))
+        while any(self.flushed.get(g, -1) < last_batch for g in self.inboxes):
+            self._next_event(timeout=self._timeout)
+        self._drain_events()
+        rest = []
+        while not self.losses.empty():
+            b, l = self.losses.get()
+            self._losses_returned = b
+            rest.append(l)
+        return rest
 
     def stop(self, last_batch: int) -> List[float]:
         from .engine import StopMsg

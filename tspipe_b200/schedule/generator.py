@@ -125,11 +125,15 @@ class ScheduleSpec:
         return max(0, head_ssl - self.n_ubatch)   # items [U, 2U) of the SSL order are view 1
 
 
-def batch_block(spec: ScheduleSpec, stage: int, batch: int, last_batch: Optional[int] = None) -> List[Op]:
+def batch_block(spec: ScheduleSpec, stage: int, batch: int, last_batch: Optional[int] = None,
+                fill: Optional[bool] = None) -> List[Op]:
     """Ordered ops of stage ``stage`` attributed to ``batch``.
 
     ``last_batch`` (set once the feeder has stopped) removes the look-ahead teacher
-    forwards of a batch that will never be fed.
+    forwards of a batch that will never be fed.  ``fill`` marks a batch whose teacher
+    forwards were not produced as look-ahead of the previous block (the first pipelined
+    batch, or the first batch after the pipeline was flushed); default: the first
+    pipelined batch only.
     """
     last = stage == spec.n_stages - 1
     ops: List[Op] = []
@@ -138,7 +142,9 @@ def batch_block(spec: ScheduleSpec, stage: int, batch: int, last_batch: Optional
     if spec.is_sync_batch(batch):
         return (spec.teacher_items(batch, stage) + spec.student_items(batch, stage) + loss
                 + spec.backward_items(batch, stage) + opt)
-    if batch == spec.skip_staleness + 1:
+    if fill is None:
+        fill = batch == spec.skip_staleness + 1
+    if fill:
         ops += spec.teacher_items(batch, stage)        # pipeline fill: nothing earlier produced T(b)
     ops += spec.student_items(batch, stage)
     nxt = spec.teacher_items(batch + 1, stage) if (last_batch is None or batch + 1 <= last_batch) else []

@@ -171,8 +171,6 @@ class TSPipe:
         self._epoch_forced: set = set()
         self.last_batch_idx = 0
         self._losses_returned = 0
-        self._shape_epoch = 0
-        self._last_shape: Any = None
         self._stopped = False
         self._feed_stream = None
 
@@ -326,8 +324,14 @@ class TSPipe:
             assert view_target is None, "Self-supervised learning does not support labels."
         sg = self.scatter_gather_fn
         ga = int(self.config["optimizer"]["gradient_accumulation"])
-        bs = sg.batch_size(view_1)
-        assert bs == sg.batch_size(view_2)
+        if view_1 is None:
+            # launcher mode: a rank that holds neither stage 0 nor the loss stage has nothing to feed
+            assert self.mode == "launcher" and not self.topo.is_first and ga == 1, \
+                "views may be omitted only on ranks that do not hold stage 0 (and without gradient accumulation)"
+            bs = 0
+        else:
+            bs = sg.batch_size(view_1)
+            assert bs == sg.batch_size(view_2)
         if ga > 1 and bs >= 4 * self.num_ubatches * ga:
             minis_1 = [b.value for b in sg.scatter(view_1, ga)]
             minis_2 = [b.value for b in sg.scatter(view_2, ga)]
@@ -338,18 +342,13 @@ class TSPipe:
         for v1, v2, vt in zip(minis_1, minis_2, minis_t):
             bid = self.batch_q.get_new_batch_id()
             self.last_batch_idx = bid
-            shape = _shape_signature((v1, v2, vt))
-            if shape != self._last_shape:
-                if self._last_shape is not None:
-                    self._shape_epoch += 1
-                self._last_shape = shape
             self._submit(bid, [v1, v2], vt)
             loss = self.wait_forward()
         return loss
 
     def _submit(self, bid: int, views: List[Any], labels: Any) -> None:
         from .runtime.engine import FeedMsg
-        msg = FeedMsg(batch_id=bid, shape_epoch=self._shape_epoch,
+        msg = FeedMsg(batch_id=bid,
                       new_lr=self.scheduled_lr_update.pop(bid, None),
                       new_momentum=self.scheduled_momentum_update.pop(bid, None), epoch=self.epoch)
         if self.mode == "spawn":
@@ -414,6 +413,27 @@ class TSPipe:
             return float(host)
         return float(item)
 
+    def flush(self) -> List[float]:
+        """Finish every fed batch and leave the pipeline idle but alive (the next ``feed`` refills it).
+        Returns the losses not yet handed out.  Launcher mode: collective over all ranks."""
+        if self.mode == "spawn":
+            return self.pipeline.flush(self.last_batch_idx)
+        from .runtime.engine import FlushMsg
+        import threading
+        done = threading.Event()
+        self.engine.on_flushed = lambda b: done.set()
+        self.engine.inbox.put(FlushMsg(self.last_batch_idx))
+        while not done.wait(0.05):
+            if self.engine.error is not None:
+                self.engine.join()
+        rest = []
+        while True:
+            l = self._pop_loss(block=False)
+            if l is None:
+                break
+            rest.append(l)
+        return rest
+
     def stop(self) -> List[float]:
         """Finish every fed batch, stop the workers, and bring the final networks back.
 
@@ -464,5 +484,3 @@ def _cpu_state(module: nn.Module) -> Dict[str, torch.Tensor]:
     return {k: v.detach().cpu().clone() for k, v in module.state_dict().items()}
 
 
-def _shape_signature(obj: Any):
-    return tuple((tuple(t.shape), t.dtype) for t in pt.tensors_of(list(obj)))
