@@ -1,0 +1,189 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def test_library_loads_and_exports():
+    from tspipe_b200.ops import fused
+    L = fused.lib()
+    assert hasattr(L, "tsp_ema_update") and hasattr(L, "tsp_lars_step")
+
+
+@pytest.mark.parametrize("n", [64, 4096 + 64, 1 << 20])
+def test_ema_update(n):
+    from tspipe_b200.ops import fused
+    torch.manual_seed(0)
+    t = torch.randn(n, device=_dev())
+    s = torch.randn(n, device=_dev())
+    want = t * 0.99 + s * 0.01
+    shadow = torch.empty(n, dtype=torch.bfloat16, device=_dev())
+    fused.ema_update_(t, s, 0.99, shadow)
+    torch.testing.assert_close(t, want, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(shadow.float(), want, rtol=1e-2, atol=1e-2)
+
+
+def _make_flat(shapes):
+    from tspipe_b200.runtime.state import FlatParams
+    ps = [torch.nn.Parameter(torch.randn(s, device=_dev())) for s in shapes]
+    flat = FlatParams(ps, _dev(), with_grad=True)
+    flat.grad.copy_(torch.randn_like(flat.grad))
+    for i, p in enumerate(ps):       # padding must stay zero
+        pass
+    return ps, flat
+
+
+SHAPES = [(64, 3, 7, 7), (64,), (64,), (256, 64, 1, 1), (1000, 333), (17,), (5, 5)]
+
+
+@pytest.mark.parametrize("opt_name", ["lars", "adamw", "sgd"])
+def test_flat_optimizers_match_per_tensor_reference(opt_name):
+    from tspipe_b200.optim import LARS, SGD, AdamW
+    import copy
+    torch.manual_seed(1)
+    ps, flat = _make_flat(SHAPES)
+    ref_ps = [torch.nn.Parameter(p.detach().clone()) for p in ps]
+    mk = {"lars": lambda q: LARS(q, lr=0.3, weight_decay=1e-3, momentum=0.9),
+          "adamw": lambda q: AdamW(q, lr=1e-2, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.05),
+          "sgd": lambda q: SGD(q, lr=0.05, momentum=0.9, nesterov=True, weight_decay=1e-4)}[opt_name]
+    opt, ref = mk(ps), mk(ref_ps)
+    opt.bind_flat(flat, use_kernel=True)
+    teacher = torch.randn(flat.total, device=_dev())
+    ref_teacher = teacher.clone()
+    opt.teacher_flat, opt.ema_momentum = teacher, 0.9
+    for step in range(3):
+        g = torch.randn_like(flat.grad)
+        flat.grad.copy_(g)
+        for i, (p, q) in enumerate(zip(ps, ref_ps)):
+            q.grad = flat._view(flat.grad, i, p.data).detach().clone()
+        opt.step()
+        ref.step()
+        for i, (p, q) in enumerate(zip(ps, ref_ps)):
+            torch.testing.assert_close(p.detach(), q.detach(), rtol=2e-5, atol=2e-6)
+            tv = flat._view(ref_teacher, i, p.data)
+            tv.mul_(0.9).add_(q.detach(), alpha=0.1)
+    for i, p in enumerate(ps):
+        torch.testing.assert_close(flat._view(teacher, i, p.data), flat._view(ref_teacher, i, p.data),
+                                   rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,d", [(1024, 256), (37, 100)])
+def test_byol_loss(dtype, n, d):
+    from tspipe_b200.losses import regression_loss
+    from tspipe_b200.ops import fused
+    torch.manual_seed(2)
+    o1 = torch.randn(n, d, device=_dev(), dtype=dtype, requires_grad=True)
+    o2 = torch.randn(n, d, device=_dev(), dtype=dtype, requires_grad=True)
+    t1 = torch.randn(n, d, device=_dev(), dtype=dtype)
+    t2 = torch.randn(n, d, device=_dev(), dtype=dtype)
+    loss = fused.byol_loss(o1, o2, t1, t2)
+    loss.backward()
+    r1 = o1.detach().float().requires_grad_()
+    r2 = o2.detach().float().requires_grad_()
+    ref = (regression_loss(r1, t2.float()) + regression_loss(r2, t1.float())).mean()
+    ref.backward()
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-4)
+    torch.testing.assert_close(loss, ref.detach(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(o1.grad.float(), r1.grad, **tol)
+    torch.testing.assert_close(o2.grad.float(), r2.grad, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,c", [(64, 10), (256, 1000), (9, 30522)])
+def test_kd_soft_target_loss(dtype, n, c):
+    from tspipe_b200.ops import fused
+    torch.manual_seed(3)
+    s = (torch.randn(n, c, device=_dev()) * 2).to(dtype).requires_grad_()
+    t = (torch.randn(n, c, device=_dev()) * 2).to(dtype)
+    y = torch.randint(0, c, (n,), device=_dev())
+    T, alpha = 4.0, 0.9
+    loss = fused.kd_soft_target_loss(s, t, y, T, alpha)
+    loss.backward()
+    r = s.detach().float().requires_grad_()
+    ref = (1 - alpha) * F.cross_entropy(r, y) + alpha * T * T * F.kl_div(
+        F.log_softmax(r / T, 1), F.softmax(t.float() / T, 1), reduction="batchmean")
+    ref.backward()
+    torch.testing.assert_close(loss, ref.detach(), rtol=2e-4, atol=1e-5)
+    tol = dict(rtol=1e-3, atol=1e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=1e-5)
+    torch.testing.assert_close(s.grad.float(), r.grad, **tol)
+
+
+def test_cross_entropy_with_ignored_rows():
+    from tspipe_b200.ops import fused
+    torch.manual_seed(4)
+    s = torch.randn(50, 97, device=_dev(), requires_grad=True)
+    y = torch.randint(0, 97, (50,), device=_dev())
+    y[::3] = -100
+    n_valid = int((y >= 0).sum())
+    loss = fused.kd_ce_loss(s, None, y, 1.0, 1.0 / n_valid, 0.0)
+    loss.backward()
+    r = s.detach().clone().requires_grad_()
+    ref = F.cross_entropy(r, y, ignore_index=-100)
+    ref.backward()
+    torch.testing.assert_close(loss, ref.detach(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(s.grad, r.grad, rtol=1e-4, atol=1e-6)
+
+
+def test_cosine_embedding_loss_masked():
+    from tspipe_b200.ops import fused
+    torch.manual_seed(5)
+    x = torch.randn(40, 768, device=_dev(), requires_grad=True)
+    y = torch.randn(40, 768, device=_dev())
+    m = torch.rand(40, device=_dev()) > 0.3
+    k = int(m.sum())
+    loss = fused.cosine_embedding_loss(x, y, 1.0 / k, m)
+    loss.backward()
+    r = x.detach().clone().requires_grad_()
+    ref = F.cosine_embedding_loss(r[m], y[m], torch.ones(k, device=_dev()))
+    ref.backward()
+    torch.testing.assert_close(loss, ref.detach(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(x.grad, r.grad, rtol=1e-3, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,d", [(197 * 4, 768), (33, 1024), (5, 64)])
+def test_layer_norm(dtype, rows, d):
+    from tspipe_b200.ops import fused
+    torch.manual_seed(6)
+    x = torch.randn(rows, d, device=_dev()).to(dtype).requires_grad_()
+    w = torch.randn(d, device=_dev(), requires_grad=True)
+    b = torch.randn(d, device=_dev(), requires_grad=True)
+    g = torch.randn(rows, d, device=_dev()).to(dtype)
+    y = fused.layer_norm(x, w, b, 1e-6)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr, br = w.detach().clone().requires_grad_(), b.detach().clone().requires_grad_()
+    yr = F.layer_norm(xr, (d,), wr, br, 1e-6)
+    yr.backward(g.float())
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(y.float(), yr.detach(), **tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
+    wtol = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=5e-2, atol=0.3)
+    torch.testing.assert_close(w.grad, wr.grad, **wtol)
+    torch.testing.assert_close(b.grad, br.grad, **wtol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gelu_bias(dtype):
+    from tspipe_b200.ops import fused
+    torch.manual_seed(7)
+    x = torch.randn(64, 3072, device=_dev()).to(dtype).requires_grad_()
+    b = torch.randn(3072, device=_dev(), requires_grad=True)
+    g = torch.randn(64, 3072, device=_dev()).to(dtype)
+    y = fused.gelu(x, b)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    brf = b.detach().clone().requires_grad_()
+    yr = F.gelu(xr + brf)
+    yr.backward(g.float())
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(y.float(), yr.detach(), **tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
+    torch.testing.assert_close(b.grad, brf.grad, rtol=2e-2, atol=0.2 if dtype == torch.bfloat16 else 1e-3)
