@@ -266,4 +266,49 @@ int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int
   return TSP_LAUNCH_CHECK();
 }
 
+// ---------------------------------------------------------------------------------------------
+// LayerNorm backward for callers that must not allocate (see tspipe_noalloc.h).
+// The per-block dw/db partial sums go to this fixed array instead of a caller-provided buffer.
+// Every GPU that loads the library holds these 1.16 MiB until the process exits.
+// ---------------------------------------------------------------------------------------------
+#include "tspipe_noalloc.h"
+
+static __device__ __align__(256) float g_ln_bwd_scratch[TSP_NOALLOC_LN_MAX_BLOCKS * 2 * TSP_NOALLOC_LN_MAX_D];
+
+int tsp_layernorm_bwd_noalloc(const void* dy, const void* x, const float* w, const float* mean, const float* rstd,
+                              void* dx, float* dw, float* db, int rows, int d, int dtype, cudaStream_t stream) {
+  // In host code `g_ln_bwd_scratch` is only a handle for the runtime, not an address a kernel can use: the
+  // device address has to be looked up, once per device, with that device current.
+  static float* scratch_of_device[TSP_NOALLOC_MAX_DEVICES] = {nullptr};
+  if (rows < 0 || d <= 0) return -3;
+  if (rows == 0) return 0;
+  if (d % 8 != 0) return -3;
+  if (d > TSP_NOALLOC_LN_MAX_D) return TSP_NOALLOC_ERR_TOO_LARGE;
+  if (dtype != TSP_DTYPE_F32 && dtype != TSP_DTYPE_BF16) return -3;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= TSP_NOALLOC_MAX_DEVICES) return TSP_NOALLOC_ERR_TOO_LARGE;
+  float* scratch = scratch_of_device[dev];
+  if (scratch == nullptr) {
+    e = cudaGetSymbolAddress((void**)&scratch, g_ln_bwd_scratch);
+    if (e != cudaSuccess) return (int)e;
+    scratch_of_device[dev] = scratch;
+  }
+  int nb = tsp_layernorm_bwd_blocks(rows);
+  if (nb > TSP_NOALLOC_LN_MAX_BLOCKS) nb = TSP_NOALLOC_LN_MAX_BLOCKS;
+  const int rpb = (rows + nb - 1) / nb;
+  const size_t smem = sizeof(float) * 2 * (size_t)d;
+  // Nothing in the scratch has to start at zero: each of the nb blocks overwrites its whole 2*d slice and the
+  // reduction reads exactly those nb slices, so what an earlier call left behind is never read.
+  if (dtype == TSP_DTYPE_BF16)
+    ln_bwd_kernel<__nv_bfloat16><<<nb, 128, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, mean,
+                                                            rstd, (__nv_bfloat16*)dx, scratch, rows, d, rpb);
+  else
+    ln_bwd_kernel<float><<<nb, 128, smem, stream>>>((const float*)dy, (const float*)x, w, mean, rstd, (float*)dx,
+                                                    scratch, rows, d, rpb);
+  ln_bwd_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, stream>>>(scratch, nb, d, dw, db);
+  return TSP_LAUNCH_CHECK();
+}
+
 }  // extern "C"
