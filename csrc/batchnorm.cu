@@ -1,0 +1,393 @@
+// Microbatch BatchNorm for channels-last activations, fused with ReLU and the residual add (sm_100a).
+//
+// Reference: `tspipe/batchnorm.py:45-120` - F.batch_norm on the microbatch plus two extra full reductions
+// (`input.sum`, `(input**2).sum`) for the deferred running statistics, followed by separate ReLU and
+// residual-add kernels in the ResNet blocks (`benchmarks/byol/models/resnet_base_network.py`).  On B200 those
+// memory-bound passes take more time than the convolutions.  Here:
+//   forward  = statistics pass (per-channel sum / sum of squares; these ARE the deferred accumulators)
+//              + one pass y = relu(scale*x + shift [+ residual]);
+//   backward = reduction pass (sum dy', sum dy'*xhat with dy' = dy masked by y > 0; writes dy' as the residual
+//              gradient when there is a residual) + one pass for dx.
+// x is viewed as [M, C] with C contiguous (NHWC or [N, C]); C % 8 == 0; statistics in fp32.
+#include "common.cuh"
+#include "tspipe_kernels.h"
+
+namespace {
+
+constexpr int kBlock = 256;
+
+struct Tile {
+  int tx_n;   // threads along the channel-vector axis
+  int ty_n;   // rows processed in parallel by a block
+};
+
+__host__ __device__ inline Tile make_tile(int cpv) {
+  Tile t;
+  t.tx_n = cpv < kBlock ? cpv : kBlock;
+  t.ty_n = kBlock / t.tx_n;
+  if (t.ty_n < 1) t.ty_n = 1;
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-channel sums:  out[c] += sum_rows a(r,c),  out[C + c] += sum_rows b(r,c)
+//   MODE 0 (forward statistics): a = x, b = x*x
+//   MODE 1 (backward reduction): a = dy', b = dy' * (x - mean) * rstd with dy' = dy masked by the ReLU:
+//          mask from y > 0 when `y` is given (residual case), else recomputed as scale*x + shift > 0 when
+//          `relu` is set (no extra tensor read); optionally stores dy' to dres.
+// grid = (row blocks, channel slabs); block = tx_n * ty_n threads; smem = ty_n * tx_n * 16 floats.
+// ---------------------------------------------------------------------------------------------
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kBlock) bn_colsum_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                                           const T* __restrict__ y, T* __restrict__ dres,
+                                                           const float* __restrict__ mean_rstd,
+                                                           const float* __restrict__ w, const float* __restrict__ bias,
+                                                           int relu, int64_t m, int c, float* __restrict__ out) {
+  extern __shared__ float sm[];
+  const int cpv = c >> 3;
+  const Tile tl = make_tile(cpv);
+  const int tx = threadIdx.x % tl.tx_n, ty = threadIdx.x / tl.tx_n;
+  const int cg = blockIdx.y * tl.tx_n + tx;
+  const bool active = (ty < tl.ty_n) && (cg < cpv);
+  float a[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { a[e] = 0.f; b[e] = 0.f; }
+  float mu[8], rs[8], sc[8], sh[8];
+  const bool recompute_mask = (MODE == 1) && relu && (y == nullptr);
+  if (MODE == 1 && active) {
+    tsp::ld8(mean_rstd, (int64_t)cg * 8, mu);
+    tsp::ld8(mean_rstd + c, (int64_t)cg * 8, rs);
+    if (recompute_mask) {
+      float wv[8], bv[8];
+      tsp::ld8(w, (int64_t)cg * 8, wv);
+      tsp::ld8(bias, (int64_t)cg * 8, bv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { sc[e] = wv[e] * rs[e]; sh[e] = bv[e] - mu[e] * sc[e]; }
+    }
+  }
+  if (active) {
+    const int64_t step = (int64_t)gridDim.x * tl.ty_n;
+    const int64_t col = (int64_t)cg * 8;
+    int64_t r = (int64_t)blockIdx.x * tl.ty_n + ty;
+    if (MODE == 0) {
+      // four independent 16-byte loads in flight per thread
+      for (; r + 3 * step < m; r += 4 * step) {
+        float v0[8], v1[8], v2[8], v3[8];
+        tsp::ld8(x, r * c + col, v0);
+        tsp::ld8(x, (r + step) * c + col, v1);
+        tsp::ld8(x, (r + 2 * step) * c + col, v2);
+        tsp::ld8(x, (r + 3 * step) * c + col, v3);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          a[e] += (v0[e] + v1[e]) + (v2[e] + v3[e]);
+          b[e] += (v0[e] * v0[e] + v1[e] * v1[e]) + (v2[e] * v2[e] + v3[e] * v3[e]);
+        }
+      }
+      for (; r < m; r += step) {
+        float v0[8];
+        tsp::ld8(x, r * c + col, v0);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { a[e] += v0[e]; b[e] += v0[e] * v0[e]; }
+      }
+    } else {
+      for (; r < m; r += 2 * step) {
+        const bool two = r + step < m;
+        const int64_t off0 = r * c + col, off1 = (r + step) * c + col;
+        float x0[8], x1[8], g0[8], g1[8], y0[8], y1[8];
+        tsp::ld8(x, off0, x0);
+        tsp::ld8(dy, off0, g0);
+        if (y != nullptr) tsp::ld8(y, off0, y0);
+        if (two) {
+          tsp::ld8(x, off1, x1);
+          tsp::ld8(dy, off1, g1);
+          if (y != nullptr) tsp::ld8(y, off1, y1);
+        }
+        if (y != nullptr) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { g0[e] = y0[e] > 0.f ? g0[e] : 0.f; if (two) g1[e] = y1[e] > 0.f ? g1[e] : 0.f; }
+        } else if (recompute_mask) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            g0[e] = (x0[e] * sc[e] + sh[e]) > 0.f ? g0[e] : 0.f;
+            if (two) g1[e] = (x1[e] * sc[e] + sh[e]) > 0.f ? g1[e] : 0.f;
+          }
+        }
+        if (dres != nullptr) { tsp::st8(dres, off0, g0); if (two) tsp::st8(dres, off1, g1); }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          a[e] += g0[e]; b[e] += g0[e] * (x0[e] - mu[e]) * rs[e];
+          if (two) { a[e] += g1[e]; b[e] += g1[e] * (x1[e] - mu[e]) * rs[e]; }
+        }
+      }
+    }
+  }
+  // reduce over ty through shared memory, then one atomic per channel per block
+  float* mine = sm + ((int64_t)ty * tl.tx_n + tx) * 16;
+  if (ty < tl.ty_n) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { mine[e] = a[e]; mine[8 + e] = b[e]; }
+  }
+  __syncthreads();
+  if (ty == 0 && cg < cpv) {
+    for (int k = 1; k < tl.ty_n; ++k) {
+      const float* o = sm + ((int64_t)k * tl.tx_n + tx) * 16;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[e] += o[e]; b[e] += o[8 + e]; }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      atomicAdd(out + cg * 8 + e, a[e]);
+      atomicAdd(out + c + cg * 8 + e, b[e]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward apply: y = act(scale*x + shift [+ res]).
+//   training: mean/var from `sums` (sum, sum of squares over m rows); block 0 saves mean / rstd and folds the
+//             sums into the deferred accumulators (acc_sum, acc_sumsq) when given.
+//   eval:     mean/var from `fixed` ([mean | var]).
+// dynamic smem: 2*c floats (scale | shift).  A thread's channel group is loop-invariant whenever the grid
+// stride is a multiple of c/8 (all power-of-two widths), so scale/shift then stay in registers.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kBlock) bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                                                          T* __restrict__ y, const float* __restrict__ sums,
+                                                          const float* __restrict__ fixed,
+                                                          const float* __restrict__ w, const float* __restrict__ b,
+                                                          float* __restrict__ save_mean_rstd,
+                                                          float* __restrict__ acc_sum, float* __restrict__ acc_sumsq,
+                                                          int64_t m, int c, float eps, int relu) {
+  extern __shared__ float sm[];
+  float* scale = sm;
+  float* shift = sm + c;
+  const float inv_m = 1.f / (float)m;
+  for (int i = threadIdx.x; i < c; i += blockDim.x) {
+    float mean, var;
+    if (fixed != nullptr) {
+      mean = fixed[i]; var = fixed[c + i];
+    } else {
+      const float s = sums[i], q = sums[c + i];
+      mean = s * inv_m;
+      var = fmaxf(q * inv_m - mean * mean, 0.f);
+      if (blockIdx.x == 0) {
+        if (acc_sum != nullptr) { acc_sum[i] += s; acc_sumsq[i] += q; }
+      }
+    }
+    const float rstd = rsqrtf(var + eps);
+    if (blockIdx.x == 0 && save_mean_rstd != nullptr) { save_mean_rstd[i] = mean; save_mean_rstd[c + i] = rstd; }
+    const float sc = (w ? w[i] : 1.f) * rstd;
+    scale[i] = sc;
+    shift[i] = (b ? b[i] : 0.f) - mean * sc;
+  }
+  __syncthreads();
+  const int cpv = c >> 3;
+  const int64_t nvec = m * cpv;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  int cg = (int)(i % cpv);
+  const int dcg = (int)(stride % cpv);
+  float sc[8], sh[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { sc[e] = scale[cg * 8 + e]; sh[e] = shift[cg * 8 + e]; }
+  for (; i < nvec; i += stride) {
+    float v[8], o[8];
+    tsp::ld8(x, i * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = v[e] * sc[e] + sh[e];
+    if (res != nullptr) {
+      float r[8];
+      tsp::ld8(res, i * 8, r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] += r[e];
+    }
+    if (relu) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = fmaxf(o[e], 0.f);
+    }
+    tsp::st8(y, i * 8, o);
+    if (dcg != 0) {
+      cg += dcg;
+      if (cg >= cpv) cg -= cpv;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { sc[e] = scale[cg * 8 + e]; sh[e] = shift[cg * 8 + e]; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward apply: dx = w*rstd * (dy' - sum(dy')/m - xhat * sum(dy'*xhat)/m), dy' masked as in the reduction
+// (by y > 0 when `y` is given, by scale*x + shift > 0 when `relu` is set and y is null).
+// Per element: dx = A*dy' + B*x + D with A = w*rstd, B = -A*rstd*k2, D = -A*k1 - B*mean.
+// dynamic smem: 5*c floats (A | B | D | scale | shift)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                              const T* __restrict__ y,
+                                                              const float* __restrict__ mean_rstd,
+                                                              const float* __restrict__ w,
+                                                              const float* __restrict__ bias, int relu,
+                                                              const float* __restrict__ sums, T* __restrict__ dx,
+                                                              int64_t m, int c) {
+  extern __shared__ float sm[];
+  float* s_a = sm;
+  float* s_b = sm + c;
+  float* s_d = sm + 2 * c;
+  float* s_sc = sm + 3 * c;
+  float* s_sh = sm + 4 * c;
+  const float inv_m = 1.f / (float)m;
+  const bool recompute_mask = relu && (y == nullptr);
+  for (int i = threadIdx.x; i < c; i += blockDim.x) {
+    const float mean = mean_rstd[i], rs = mean_rstd[c + i];
+    const float k1 = sums[i] * inv_m, k2 = sums[c + i] * inv_m;
+    const float wv = w ? w[i] : 1.f;
+    const float A = wv * rs;
+    const float B = -A * rs * k2;
+    s_a[i] = A;
+    s_b[i] = B;
+    s_d[i] = -A * k1 - B * mean;
+    s_sc[i] = A;
+    s_sh[i] = (bias ? bias[i] : 0.f) - mean * A;
+  }
+  __syncthreads();
+  const int cpv = c >> 3;
+  const int64_t nvec = m * cpv;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  int cg = (int)(i % cpv);
+  const int dcg = (int)(stride % cpv);
+  float A[8], B[8], D[8], sh[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { A[e] = s_a[cg * 8 + e]; B[e] = s_b[cg * 8 + e]; D[e] = s_d[cg * 8 + e]; sh[e] = s_sh[cg * 8 + e]; }
+  for (; i < nvec; i += stride) {
+    float g[8], xv[8], o[8];
+    tsp::ld8(dy, i * 8, g);
+    tsp::ld8(x, i * 8, xv);
+    if (y != nullptr) {
+      float yv[8];
+      tsp::ld8(y, i * 8, yv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = yv[e] > 0.f ? g[e] : 0.f;
+    } else if (recompute_mask) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = (xv[e] * A[e] + sh[e]) > 0.f ? g[e] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = A[e] * g[e] + B[e] * xv[e] + D[e];
+    tsp::st8(dx, i * 8, o);
+    if (dcg != 0) {
+      cg += dcg;
+      if (cg >= cpv) cg -= cpv;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { A[e] = s_a[cg * 8 + e]; B[e] = s_b[cg * 8 + e]; D[e] = s_d[cg * 8 + e]; sh[e] = s_sh[cg * 8 + e]; }
+    }
+  }
+}
+
+inline int row_blocks(int64_t m, int ty_n, int slabs) {
+  int64_t want = (m + ty_n - 1) / ty_n;
+  int64_t cap = (148 * 8) / (slabs > 0 ? slabs : 1);
+  if (cap < 1) cap = 1;
+  // keep at least ~32 rows per thread-row so that the atomics stay a small part of the work
+  int64_t by_work = (m + (int64_t)ty_n * 32 - 1) / ((int64_t)ty_n * 32);
+  if (by_work < 1) by_work = 1;
+  int64_t g = want < cap ? want : cap;
+  if (g > by_work) g = by_work;
+  return (int)(g < 1 ? 1 : g);
+}
+
+inline int elem_blocks(int64_t nvec) {
+  int64_t b = (nvec + kBlock - 1) / kBlock;
+  if (b > 148 * 16) b = 148 * 16;
+  return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace
+
+extern "C" {
+
+// sums [2*c] fp32 is zeroed here, then receives per-channel sum(x) and sum(x^2).
+int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (c % 8 != 0 || c > 8192) return -3;
+  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c, stream);
+  if (e != cudaSuccess) return (int)e;
+  const int cpv = c / 8;
+  const Tile tl = make_tile(cpv);
+  const int slabs = (cpv + tl.tx_n - 1) / tl.tx_n;
+  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs);
+  const size_t smem = sizeof(float) * 16 * (size_t)tl.tx_n * tl.ty_n;
+  if (dtype == TSP_DTYPE_BF16)
+    bn_colsum_kernel<__nv_bfloat16, 0><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, nullptr, nullptr, nullptr,
+                                                                       nullptr, nullptr, nullptr, 0, m, c, sums);
+  else
+    bn_colsum_kernel<float, 0><<<grid, kBlock, smem, stream>>>((const float*)x, nullptr, nullptr, nullptr, nullptr, nullptr,
+                                                               nullptr, 0, m, c, sums);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
+                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq, int64_t m,
+                 int c, float eps, int relu, int dtype, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (c % 8 != 0 || c > 4096) return -3;
+  const size_t smem = sizeof(float) * 2 * (size_t)c;
+  const int grid = elem_blocks(m * (c / 8));
+  if (dtype == TSP_DTYPE_BF16)
+    bn_apply_kernel<__nv_bfloat16><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
+                                                                   (__nv_bfloat16*)y, sums, fixed_mean_var, w, b,
+                                                                   save_mean_rstd, acc_sum, acc_sumsq, m, c, eps, relu);
+  else
+    bn_apply_kernel<float><<<grid, kBlock, smem, stream>>>((const float*)x, (const float*)res, (float*)y, sums,
+                                                           fixed_mean_var, w, b, save_mean_rstd, acc_sum, acc_sumsq, m,
+                                                           c, eps, relu);
+  return TSP_LAUNCH_CHECK();
+}
+
+// sums [2*c] is zeroed, then receives sum(dy') and sum(dy' * xhat) (= db and dw).  `y` non-null applies the ReLU
+// mask; `dres` non-null receives dy'.
+int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, const float* mean_rstd, const float* w,
+                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (c % 8 != 0 || c > 8192) return -3;
+  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c, stream);
+  if (e != cudaSuccess) return (int)e;
+  const int cpv = c / 8;
+  const Tile tl = make_tile(cpv);
+  const int slabs = (cpv + tl.tx_n - 1) / tl.tx_n;
+  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs);
+  const size_t smem = sizeof(float) * 16 * (size_t)tl.tx_n * tl.ty_n;
+  if (dtype == TSP_DTYPE_BF16)
+    bn_colsum_kernel<__nv_bfloat16, 1><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+                                                                       (const __nv_bfloat16*)y, (__nv_bfloat16*)dres,
+                                                                       mean_rstd, w, bias, relu, m, c, sums);
+  else
+    bn_colsum_kernel<float, 1><<<grid, kBlock, smem, stream>>>((const float*)x, (const float*)dy, (const float*)y,
+                                                               (float*)dres, mean_rstd, w, bias, relu, m, c, sums);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean_rstd, const float* w,
+                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype,
+                     cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (c % 8 != 0 || c > 4096) return -3;
+  const size_t smem = sizeof(float) * 5 * (size_t)c;
+  if (smem > 48 * 1024) {      // opt in to more than the default dynamic shared memory
+    cudaFuncSetAttribute(bn_bwd_apply_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    cudaFuncSetAttribute(bn_bwd_apply_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+  }
+  const int grid = elem_blocks(m * (c / 8));
+  if (dtype == TSP_DTYPE_BF16)
+    bn_bwd_apply_kernel<__nv_bfloat16><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                       (const __nv_bfloat16*)y, mean_rstd, w, bias, relu,
+                                                                       sums, (__nv_bfloat16*)dx, m, c);
+  else
+    bn_bwd_apply_kernel<float><<<grid, kBlock, smem, stream>>>((const float*)dy, (const float*)x, (const float*)y,
+                                                               mean_rstd, w, bias, relu, sums, (float*)dx, m, c);
+  return TSP_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -45,6 +45,17 @@ int tsp_gelu_fwd(const void* x, const float* bias, void* y, int64_t n, int d, in
 int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int64_t n, int d, int dtype,
                  cudaStream_t stream);
 
+// ---- batchnorm.cu -----------------------------------------------------------------------------------------------
+int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
+int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
+                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq, int64_t m,
+                 int c, float eps, int relu, int dtype, cudaStream_t stream);
+int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, const float* mean_rstd, const float* w,
+                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
+int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean_rstd, const float* w,
+                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype,
+                     cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

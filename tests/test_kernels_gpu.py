@@ -187,3 +187,62 @@ def test_gelu_bias(dtype):
     torch.testing.assert_close(y.float(), yr.detach(), **tol)
     torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
     torch.testing.assert_close(b.grad, brf.grad, rtol=2e-2, atol=0.2 if dtype == torch.bfloat16 else 1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,residual,relu", [((8, 64, 14, 14), True, True), ((4, 256, 7, 7), False, True),
+                                                ((16, 24, 5, 3), False, False), ((32, 512), False, True),
+                                                ((3, 2048, 2, 2), True, True)])
+def test_fused_batchnorm_act(dtype, shape, residual, relu):
+    """Fused BN(+residual)(+ReLU) forward and backward vs. fp32 F.batch_norm + add + relu; the deferred
+    accumulators must receive the microbatch sums."""
+    from tspipe_b200.batchnorm import DeferredBatchNorm
+    from tspipe_b200.ops import bn as fbn
+    torch.manual_seed(8)
+    c = shape[1]
+    fmt = torch.channels_last if len(shape) == 4 else torch.contiguous_format
+    x = (torch.randn(shape, device=_dev()) * 1.5 + 0.3).to(dtype).contiguous(memory_format=fmt).requires_grad_()
+    res = torch.randn(shape, device=_dev()).to(dtype).contiguous(memory_format=fmt).requires_grad_() if residual else None
+    g = torch.randn(shape, device=_dev()).to(dtype).contiguous(memory_format=fmt)
+    bn = DeferredBatchNorm(c, chunks=3).to(_dev())
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.uniform_(-0.5, 0.5)
+    assert fbn.applicable(bn, x)
+    y = fbn.bn_act(bn, x, res, relu)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    rr = res.detach().float().requires_grad_() if residual else None
+    wr, br = bn.weight.detach().clone().requires_grad_(), bn.bias.detach().clone().requires_grad_()
+    yr = F.batch_norm(xr, None, None, wr, br, training=True, eps=bn.eps)
+    if residual:
+        yr = yr + rr
+    if relu:
+        yr = F.relu(yr)
+    yr.backward(g.float())
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(y.float(), yr.detach(), **tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
+    if residual:
+        torch.testing.assert_close(res.grad.float(), rr.grad, **tol)
+    wtol = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=5e-2, atol=0.5)
+    torch.testing.assert_close(bn.weight.grad, wr.grad, **wtol)
+    torch.testing.assert_close(bn.bias.grad, br.grad, **wtol)
+    dims = [0] + list(range(2, len(shape)))
+    xf = x.detach().float()
+    torch.testing.assert_close(bn.sum, xf.sum(dims), rtol=1e-3, atol=1e-2)
+    torch.testing.assert_close(bn.sum_squares, (xf * xf).sum(dims), rtol=1e-3, atol=1e-2)
+    assert bn.tracked == 1 and bn.counter == x.numel() // c
+
+
+def test_fused_batchnorm_eval_uses_running_stats():
+    from tspipe_b200.ops import bn as fbn
+    torch.manual_seed(9)
+    bn = torch.nn.BatchNorm2d(32).to(_dev())
+    with torch.no_grad():
+        bn.running_mean.normal_()
+        bn.running_var.uniform_(0.5, 2.0)
+    bn.eval()
+    x = torch.randn(4, 32, 6, 6, device=_dev()).contiguous(memory_format=torch.channels_last)
+    y = fbn.bn_act(bn, x, relu=True)
+    torch.testing.assert_close(y, F.relu(bn(x)), rtol=1e-4, atol=1e-5)

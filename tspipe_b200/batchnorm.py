@@ -70,6 +70,10 @@ class DeferredBatchNorm(_BatchNorm):
         self.tracked = 0
 
     def forward(self, input: Tensor) -> Tensor:  # type: ignore[override]
+        if input.is_cuda:
+            from .ops import bn as _bn
+            if _bn.applicable(self, input):
+                return _bn.bn_act(self, input)
         if not self.training:
             return F.batch_norm(input, self.running_mean, self.running_var, self.weight, self.bias,
                                 training=False, momentum=0.0, eps=self.eps)

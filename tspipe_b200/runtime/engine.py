@@ -233,6 +233,9 @@ class StageEngine:
         self.autocast = rt["dtype"] == "bf16"
         self.fused = bool(rt["fused"]) and self.cuda
         self.channels_last = bool(rt["channels_last"])
+        if self.cuda:
+            from ..ops import bn as _bn
+            _bn.set_enabled(self.fused)
 
         self.online.to(self.device)
         self.target.to(self.device)
