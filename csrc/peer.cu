@@ -1,0 +1,214 @@
+// Kernels that read or write other GPUs' memory through peer-mapped pointers (NVLink 5 / NVSwitch), sm_100a.
+//
+// The reference has no data parallelism in its runtime; its baselines use DDP's bucketed NCCL all-reduce followed
+// by a per-tensor optimizer (`benchmarks/moco-v3/main.py:249-254`, `benchmarks/byol/main.py:13-46`).  Here, with R
+// pipeline replicas, the gradient reduce-scatter, the cast/scale, the sharded LARS / AdamW step and the all-gather of
+// the updated parameters are two launches (LARS: the trust ratio needs whole-tensor norms in between) or one (AdamW):
+//   * each rank owns the flat range [lo, hi) of its stage's parameter buffer;
+//   * it sums that range of every replica's gradient buffer with plain peer loads (the reduce-scatter),
+//   * updates parameter and optimizer state of the range,
+//   * and stores the new parameters into every replica's parameter buffer with peer stores (the all-gather).
+// Ordering against the peers' backward passes and next forward passes is established by the caller with
+// stream-ordered collectives; nothing in here spins on a flag.
+#include "common.cuh"
+#include "tspipe_kernels.h"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxPeers = 8;
+
+struct PeerPtrs {
+  float* p[kMaxPeers];
+};
+
+struct ChunkView {
+  int seg;
+  int64_t begin;
+  int len;
+};
+
+__device__ __forceinline__ ChunkView load_chunk(const int64_t* __restrict__ chunks, int c) {
+  ChunkView v;
+  v.seg = (int)chunks[3 * (int64_t)c];
+  v.begin = chunks[3 * (int64_t)c + 1];
+  v.len = (int)chunks[3 * (int64_t)c + 2];
+  return v;
+}
+
+// g_out[k] = scale * sum_r grads[r][k] over the chunk; LARS norms accumulated for adaptive segments.
+__global__ void __launch_bounds__(kThreads) dp_reduce_norms_kernel(PeerPtrs grads, int n_peers, float scale,
+                                                                   float* __restrict__ g_out,
+                                                                   const float* __restrict__ p,
+                                                                   const int64_t* __restrict__ chunks,
+                                                                   const float* __restrict__ seg_hp,
+                                                                   float* __restrict__ norms) {
+  __shared__ float scratch[33];
+  const ChunkView c = load_chunk(chunks, blockIdx.x);
+  const float* hp = seg_hp + 5 * (int64_t)c.seg;
+  const bool adapt = norms != nullptr && hp[4] != 0.f;
+  const float wd = hp[1];
+  float sp = 0.f, su = 0.f;
+  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+    const int64_t k = c.begin + i;
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) s += grads.p[r][k];
+    s *= scale;
+    g_out[k] = s;
+    if (adapt) {
+      const float a = p[k], u = s + wd * a;
+      sp += a * a;
+      su += u * u;
+    }
+  }
+  if (adapt) {
+    sp = tsp::block_sum(sp, scratch);
+    su = tsp::block_sum(su, scratch);
+    if (threadIdx.x == 0) {
+      atomicAdd(norms + 2 * c.seg, sp);
+      atomicAdd(norms + 2 * c.seg + 1, su);
+    }
+  }
+}
+
+// LARS apply on the owned range (gradient already reduced into g), new parameters stored to every replica.
+__global__ void __launch_bounds__(kThreads) dp_lars_apply_kernel(PeerPtrs params, int n_peers, int self,
+                                                                 const float* __restrict__ g, float* __restrict__ mu,
+                                                                 const int64_t* __restrict__ chunks,
+                                                                 const float* __restrict__ seg_hp,
+                                                                 const float* __restrict__ norms) {
+  const ChunkView c = load_chunk(chunks, blockIdx.x);
+  const float* hp = seg_hp + 5 * (int64_t)c.seg;
+  const float lr = hp[0], wd = hp[1], mom = hp[2], trust = hp[3];
+  const bool adapt = hp[4] != 0.f;
+  float q = 1.f;
+  if (adapt) {
+    const float pn = sqrtf(norms[2 * c.seg]), un = sqrtf(norms[2 * c.seg + 1]);
+    q = (pn > 0.f && un > 0.f) ? trust * pn / un : 1.f;
+  }
+  const float wd_eff = adapt ? wd : 0.f;
+  const float* p_self = params.p[self];
+  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+    const int64_t k = c.begin + i;
+    const float pv = p_self[k];
+    const float dp = q * (g[k] + wd_eff * pv);
+    const float m2 = mom * mu[k] + dp;
+    mu[k] = m2;
+    const float np = pv - lr * m2;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) params.p[r][k] = np;
+  }
+}
+
+// AdamW: reduce + update + store to all replicas in one pass.
+__global__ void __launch_bounds__(kThreads) dp_adamw_kernel(PeerPtrs grads, PeerPtrs params, int n_peers, int self,
+                                                            float scale, float* __restrict__ m, float* __restrict__ v,
+                                                            const int64_t* __restrict__ chunks,
+                                                            const float* __restrict__ seg_hp) {
+  const ChunkView c = load_chunk(chunks, blockIdx.x);
+  const float* hp = seg_hp + 7 * (int64_t)c.seg;
+  const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6];
+  const float step = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
+  const float* p_self = params.p[self];
+  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+    const int64_t k = c.begin + i;
+    float gv = 0.f;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) gv += grads.p[r][k];
+    gv *= scale;
+    float pv = p_self[k] * (1.f - lr * wd);
+    const float mv = b1 * m[k] + (1.f - b1) * gv;
+    const float vv = b2 * v[k] + (1.f - b2) * gv * gv;
+    m[k] = mv;
+    v[k] = vv;
+    pv -= step * mv / (sqrtf(vv) * inv_sqrt_bc2 + eps);
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) params.p[r][k] = pv;
+  }
+}
+
+inline bool fill(PeerPtrs& dst, void* const* src, int n) {
+  if (n < 1 || n > kMaxPeers) return false;
+  for (int i = 0; i < kMaxPeers; ++i) dst.p[i] = i < n ? (float*)src[i] : nullptr;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Make `peer_device`'s memory addressable from kernels of the current device.  0 = ok / already enabled,
+// -5 = the two devices have no peer path.
+int tsp_enable_peer_access(int peer_device) {
+  int cur = -1;
+  cudaError_t e = cudaGetDevice(&cur);
+  if (e != cudaSuccess) return (int)e;
+  if (cur == peer_device) return 0;
+  int can = 0;
+  e = cudaDeviceCanAccessPeer(&can, cur, peer_device);
+  if (e != cudaSuccess) return (int)e;
+  if (!can) return -5;
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();
+    return 0;
+  }
+  return (int)e;
+}
+
+// Map a buffer exported by another process (64-byte CUDA IPC handle of its allocation) into the CURRENT device's
+// address space; peer access to the owning device is enabled by the runtime as part of the mapping.  The handle
+// must come from a different process.  `*base` receives the mapped allocation base (add the exporter's offset).
+int tsp_ipc_import(const unsigned char* handle64, void** base) {
+  cudaIpcMemHandle_t h;
+  for (int i = 0; i < 64; ++i) reinterpret_cast<unsigned char*>(&h)[i] = handle64[i];
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return (int)e;
+  }
+  *base = p;
+  return 0;
+}
+
+int tsp_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }
+
+int tsp_dp_reduce_norms(void* const* grads, int n_peers, float scale, float* g_out, const float* p,
+                        const int64_t* chunks, int n_chunks, const float* seg_hp, float* norms, int n_seg,
+                        cudaStream_t stream) {
+  if (n_chunks <= 0) return 0;
+  PeerPtrs gp;
+  if (!fill(gp, grads, n_peers)) return -3;
+  if (norms != nullptr) {
+    cudaError_t e = cudaMemsetAsync(norms, 0, sizeof(float) * 2 * (size_t)n_seg, stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dp_reduce_norms_kernel<<<n_chunks, kThreads, 0, stream>>>(gp, n_peers, scale, g_out, p, chunks, seg_hp, norms);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_dp_lars_apply(void* const* params, int n_peers, int self, const float* g, float* mu, const int64_t* chunks,
+                      int n_chunks, const float* seg_hp, const float* norms, cudaStream_t stream) {
+  if (n_chunks <= 0) return 0;
+  PeerPtrs pp;
+  if (!fill(pp, params, n_peers) || self < 0 || self >= n_peers) return -3;
+  dp_lars_apply_kernel<<<n_chunks, kThreads, 0, stream>>>(pp, n_peers, self, g, mu, chunks, seg_hp, norms);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_dp_adamw_step(void* const* grads, void* const* params, int n_peers, int self, float scale, float* m, float* v,
+                      const int64_t* chunks, int n_chunks, const float* seg_hp, cudaStream_t stream) {
+  if (n_chunks <= 0) return 0;
+  PeerPtrs gp, pp;
+  if (!fill(gp, grads, n_peers) || !fill(pp, params, n_peers) || self < 0 || self >= n_peers) return -3;
+  dp_adamw_kernel<<<n_chunks, kThreads, 0, stream>>>(gp, pp, n_peers, self, scale, m, v, chunks, seg_hp);
+  return TSP_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -56,6 +56,18 @@ int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* 
                      const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype,
                      cudaStream_t stream);
 
+// ---- peer.cu ------------------------------------------------------------------------------------------------------
+int tsp_enable_peer_access(int peer_device);
+int tsp_ipc_import(const unsigned char* handle64, void** base);
+int tsp_ipc_close(void* base);
+int tsp_dp_reduce_norms(void* const* grads, int n_peers, float scale, float* g_out, const float* p,
+                        const int64_t* chunks, int n_chunks, const float* seg_hp, float* norms, int n_seg,
+                        cudaStream_t stream);
+int tsp_dp_lars_apply(void* const* params, int n_peers, int self, const float* g, float* mu, const int64_t* chunks,
+                      int n_chunks, const float* seg_hp, const float* norms, cudaStream_t stream);
+int tsp_dp_adamw_step(void* const* grads, void* const* params, int n_peers, int self, float scale, float* m, float* v,
+                      const int64_t* chunks, int n_chunks, const float* seg_hp, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -246,3 +246,94 @@ def test_fused_batchnorm_eval_uses_running_stats():
     x = torch.randn(4, 32, 6, 6, device=_dev()).contiguous(memory_format=torch.channels_last)
     y = fbn.bn_act(bn, x, relu=True)
     torch.testing.assert_close(y, F.relu(bn(x)), rtol=1e-4, atol=1e-5)
+
+
+def _two_gpus():
+    return torch.cuda.device_count() >= 2
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ema_reads_student_from_peer_gpu():
+    """The momentum update kernel running on cuda:0 reads the student buffer that lives on cuda:1."""
+    from tspipe_b200.comm import peer
+    from tspipe_b200.ops import fused
+    torch.manual_seed(10)
+    n = (1 << 20) + 64
+    t = torch.randn(n, device="cuda:0")
+    s = torch.randn(n, device="cuda:1")
+    want = t.cpu() * 0.9 + s.cpu() * 0.1
+    torch.cuda.synchronize("cuda:1")
+    with torch.cuda.device(0):
+        peer.enable_peer_access(1)
+        fused.ema_update_(t, s, 0.9)
+        torch.cuda.synchronize()
+    torch.testing.assert_close(t.cpu(), want, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("opt_name", ["lars", "adamw"])
+def test_dp_fused_step_two_replicas_one_process(opt_name):
+    """Two replicas emulated in one process (buffers on cuda:0 and cuda:1, peer access on): each rank's
+    reduce-scatter + sharded step + all-gather kernels, run one after the other, must leave BOTH parameter
+    buffers equal to the per-tensor reference optimizer stepped on the averaged gradient."""
+    from tspipe_b200.comm import peer
+    from tspipe_b200.comm.peer import pointer_table
+    from tspipe_b200.ops import fused
+    from tspipe_b200.optim import LARS, AdamW
+    from tspipe_b200.runtime.state import FlatParams
+    torch.manual_seed(11)
+    devs = [torch.device("cuda", 0), torch.device("cuda", 1)]
+    base = [torch.randn(s) for s in SHAPES]
+    flats, states = [], []
+    for d in devs:
+        ps = [torch.nn.Parameter(b.clone().to(d)) for b in base]
+        flats.append(FlatParams(ps, d, with_grad=True, pad_to=2))
+    for i, d in enumerate(devs):
+        with torch.cuda.device(d):
+            peer.enable_peer_access(1 - i)
+    ref_ps = [torch.nn.Parameter(b.clone()) for b in base]
+    mk = {"lars": lambda q: LARS(q, lr=0.3, weight_decay=1e-3, momentum=0.9),
+          "adamw": lambda q: AdamW(q, lr=1e-2, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.05)}[opt_name]
+    ref = mk(ref_ps)
+    total = flats[0].total
+    shard = total // 2
+    st = [{k: torch.zeros(total, device=d) for k in ("a", "b")} for d in devs]
+    norms = [torch.zeros(2 * len(SHAPES), device=d) for d in devs]
+    for step in range(1, 3):
+        gs = [torch.randn(total) for _ in devs]
+        for f, g in zip(flats, gs):
+            f.grad.copy_(g.to(f.device))
+        avg = (gs[0] + gs[1]) / 2
+        for i, q in enumerate(ref_ps):
+            q.grad = avg[flats[0].offsets[i]: flats[0].offsets[i] + flats[0].numels[i]].view(q.shape).clone()
+        ref.step()
+        torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+        rows_l = [[0.3, 1e-3, 0.9, 0.001, 1.0 if len(s) > 1 else 0.0] for s in SHAPES]
+        rows_a = [[1e-2, 0.9, 0.98, 1e-6, 0.05, 1 - 0.9 ** step, 1 - 0.98 ** step] for _ in SHAPES]
+        gptr = pointer_table([f.grad for f in flats])
+        pptr = pointer_table([f.data for f in flats])
+        if opt_name == "lars":
+            for r, d in enumerate(devs):
+                with torch.cuda.device(d):
+                    hp = torch.tensor(rows_l, device=d)
+                    ch = fused.build_chunks(flats[r].offsets, flats[r].numels, d, r * shard, (r + 1) * shard)
+                    fused.dp_reduce_norms_(gptr, 2, 0.5, flats[r].grad, flats[r].data, ch, hp, norms[r])
+                    torch.cuda.synchronize()
+            tot = norms[0].cpu() + norms[1].cpu()            # the all-reduce of the partial norms
+            for r, d in enumerate(devs):
+                with torch.cuda.device(d):
+                    hp = torch.tensor(rows_l, device=d)
+                    ch = fused.build_chunks(flats[r].offsets, flats[r].numels, d, r * shard, (r + 1) * shard)
+                    fused.dp_lars_apply_(pptr, 2, r, flats[r].grad, st[r]["a"], ch, hp, tot.to(d))
+                    torch.cuda.synchronize()
+        else:
+            for r, d in enumerate(devs):
+                with torch.cuda.device(d):
+                    hp = torch.tensor(rows_a, device=d)
+                    ch = fused.build_chunks(flats[r].offsets, flats[r].numels, d, r * shard, (r + 1) * shard)
+                    fused.dp_adamw_step_(gptr, pptr, 2, r, 0.5, st[r]["a"], st[r]["b"], ch, hp)
+                    torch.cuda.synchronize()
+        for f in flats:
+            for i, q in enumerate(ref_ps):
+                got = f.data[f.offsets[i]: f.offsets[i] + f.numels[i]].view(q.shape).cpu()
+                torch.testing.assert_close(got, q.detach(), rtol=3e-5, atol=3e-6)

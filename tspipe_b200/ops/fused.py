@@ -70,6 +70,8 @@ def ema_update_(teacher: torch.Tensor, student: torch.Tensor, momentum: float,
     view of another GPU's memory mapped into this process."""
     assert teacher.dtype == torch.float32 and student.dtype == torch.float32
     assert teacher.is_contiguous() and student.is_contiguous() and teacher.numel() == student.numel()
+    if teacher.numel() == 0:
+        return
     with torch.cuda.device(teacher.device):
         _check(lib().tsp_ema_update(_ptr(teacher), _ptr(student), _c.c_int64(teacher.numel()),
                                     _c.c_float(momentum), _ptr(bf16_shadow), _stream()), "tsp_ema_update")
@@ -339,3 +341,39 @@ def gelu(x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
             (bias is not None and x.shape[-1] % 8 != 0):
         return torch.nn.functional.gelu(x if bias is None else x + bias)
     return _Gelu.apply(x, bias)
+
+
+# ---------------------------------------------------------------------------------------------
+# data-parallel reduce-scatter + sharded step + all-gather over peer-mapped buffers (csrc/peer.cu)
+# ---------------------------------------------------------------------------------------------
+@torch.no_grad()
+def dp_reduce_norms_(grad_ptrs, n_peers, scale, g_out, p, chunks, seg_hp, norms) -> None:
+    L = lib()
+    L.tsp_dp_reduce_norms.restype = _c.c_int
+    with torch.cuda.device(p.device):
+        _check(L.tsp_dp_reduce_norms(grad_ptrs, _c.c_int(n_peers), _c.c_float(scale), _ptr(g_out), _ptr(p),
+                                     _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp), _ptr(norms),
+                                     _c.c_int(seg_hp.shape[0]), _stream()), "tsp_dp_reduce_norms")
+    _count(2)
+
+
+@torch.no_grad()
+def dp_lars_apply_(param_ptrs, n_peers, self_idx, g, mu, chunks, seg_hp, norms) -> None:
+    L = lib()
+    L.tsp_dp_lars_apply.restype = _c.c_int
+    with torch.cuda.device(g.device):
+        _check(L.tsp_dp_lars_apply(param_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _ptr(g), _ptr(mu), _ptr(chunks),
+                                   _c.c_int(chunks.shape[0]), _ptr(seg_hp), _ptr(norms), _stream()),
+               "tsp_dp_lars_apply")
+    _count()
+
+
+@torch.no_grad()
+def dp_adamw_step_(grad_ptrs, param_ptrs, n_peers, self_idx, scale, m, v, chunks, seg_hp) -> None:
+    L = lib()
+    L.tsp_dp_adamw_step.restype = _c.c_int
+    with torch.cuda.device(m.device):
+        _check(L.tsp_dp_adamw_step(grad_ptrs, param_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _c.c_float(scale),
+                                   _ptr(m), _ptr(v), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
+                                   _stream()), "tsp_dp_adamw_step")
+    _count()

@@ -45,6 +45,28 @@ class _FlatMixin:
             self._norms = torch.zeros(2 * max(len(flat.params), 1), dtype=torch.float32, device=flat.device)
         self._hp_cache = None
 
+    def enable_dp(self, group, peer_grads, peer_params, self_index: int) -> None:
+        """Data-parallel mode over peer-mapped buffers: this rank owns ``1/R`` of the flat range; the step
+        sums that range of every replica's gradients with peer loads, updates it, and stores the new
+        parameters into every replica's buffer (``csrc/peer.cu``).  ``peer_grads`` / ``peer_params`` hold one
+        flat tensor per replica (this rank's own at ``self_index``)."""
+        from ..comm.peer import pointer_table
+        from ..ops import fused
+        assert self.flat is not None and self.use_kernel
+        r = len(peer_grads)
+        assert self.flat.total % r == 0
+        shard = self.flat.total // r
+        self._dp = dict(group=group, r=r, idx=self_index, grads=pointer_table(peer_grads),
+                        params=pointer_table(peer_params), keep=(list(peer_grads), list(peer_params)),
+                        chunks=fused.build_chunks(self.flat.offsets, self.flat.numels, self.flat.device,
+                                                  self_index * shard, (self_index + 1) * shard),
+                        token=torch.zeros(1, device=self.flat.device))
+        self.handles_dp = True
+
+    def _dp_barrier(self) -> None:
+        import torch.distributed as dist
+        dist.all_reduce(self._dp["token"], group=self._dp["group"])
+
     def _buf(self, name: str) -> torch.Tensor:
         if name not in self._flat_state:
             self._flat_state[name] = torch.zeros_like(self.flat.data)
@@ -93,6 +115,17 @@ class LARS(_FlatMixin, Optimizer):
             from ..ops import fused
             rows = [[g["lr"], g["weight_decay"], g["momentum"], g["trust_coefficient"], 1.0 if p.ndim > 1 else 0.0]
                     for p, g in zip(flat.params, self._seg_group)]
+            if self.handles_dp:
+                import torch.distributed as dist
+                d = self._dp
+                hp = self._hp_table(rows)
+                self._dp_barrier()                      # every replica's backward is complete
+                fused.dp_reduce_norms_(d["grads"], d["r"], grad_scale / d["r"], flat.grad, flat.data, d["chunks"], hp,
+                                       self._norms)
+                dist.all_reduce(self._norms, group=d["group"])     # whole-tensor norms; also: all gradient reads done
+                fused.dp_lars_apply_(d["params"], d["r"], d["idx"], flat.grad, mu, d["chunks"], hp, self._norms)
+                self._dp_barrier()                      # every replica's parameters are complete
+                return
             fused.lars_step_(flat.data, flat.grad, mu, self._chunks, self._hp_table(rows), self._norms, grad_scale,
                              self.teacher_flat, self.ema_momentum)
             return
@@ -140,6 +173,13 @@ class AdamW(_FlatMixin, Optimizer):
             from ..ops import fused
             rows = [[g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"],
                      1.0 - g["betas"][0] ** t, 1.0 - g["betas"][1] ** t] for g in self._seg_group]
+            if self.handles_dp:
+                d = self._dp
+                self._dp_barrier()
+                fused.dp_adamw_step_(d["grads"], d["params"], d["r"], d["idx"], grad_scale / d["r"], m, v, d["chunks"],
+                                     self._hp_table(rows))
+                self._dp_barrier()
+                return
             fused.adamw_step_(flat.data, flat.grad, m, v, self._chunks, self._hp_table(rows), grad_scale,
                               self.teacher_flat, self.ema_momentum)
             return

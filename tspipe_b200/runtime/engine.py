@@ -252,6 +252,8 @@ class StageEngine:
                                       pad_to=max(topo.dp, 1))
         self.flat_target = FlatParams([p for p in self.target.parameters()], self.device, with_grad=False)
         self._bind_optimizer()
+        self.dp_fused = False
+        self._enable_dp_fused()
         self.ema_plan = ema_plan
         self.updater = self._make_updater(target_update_fn)
 
@@ -304,6 +306,19 @@ class StageEngine:
         if opt is not None and hasattr(opt, "bind_flat"):
             opt.bind_flat(self.flat_online, use_kernel=self.fused)
 
+    def _enable_dp_fused(self) -> None:
+        """With pipeline replicas on CUDA, let the flat optimizer do reduce-scatter + step + all-gather in
+        its own kernels over peer-mapped gradient / parameter buffers instead of an NCCL all-reduce."""
+        opt, topo = self.optimizer, self.topo
+        if not (topo.dp > 1 and self.fused and self.cfg["runtime"].get("peer_memory", True)
+                and hasattr(opt, "enable_dp") and type(opt).__name__ in ("LARS", "AdamW")):
+            return
+        from ..comm import peer
+        grads = peer.exchange(self.flat_online.grad, topo.dp_group, topo.dp_ranks)
+        params = peer.exchange(self.flat_online.data, topo.dp_group, topo.dp_ranks)
+        opt.enable_dp(topo.dp_group, grads, params, topo.replica)
+        self.dp_fused = True
+
     def _make_updater(self, fn: Optional[Callable]) -> TeacherUpdater:
         if fn is None:
             return FrozenTeacher()
@@ -311,7 +326,8 @@ class StageEngine:
             plan = self.ema_plan
             if plan is None or plan.is_local_prefix:
                 if corresponding_prefix(self.flat_online, self.flat_target):
-                    if hasattr(self.optimizer, "bind_flat") and self.cfg["runtime"].get("fuse_ema", True):
+                    if hasattr(self.optimizer, "bind_flat") and self.cfg["runtime"].get("fuse_ema", True) \
+                            and not self.dp_fused:
                         return OptimizerFusedEma(self.optimizer, self.flat_target)
                     return FlatEmaTeacher(self.flat_target, self.flat_online.data, use_kernel=self.fused)
             else:
@@ -518,7 +534,7 @@ class StageEngine:
                 break
             self._post_forward(nxt)
         pieces = self.fwd_posted.pop(key)
-        return [_rebuild(h.wait(), others, tree, wrapped) for h, tree, wrapped, others in pieces]
+        return [(_rebuild(h.wait(), others, tree, wrapped), flags) for h, tree, wrapped, others, flags in pieces]
 
     def _fwd_keys(self, start: int = 1):
         b = start
@@ -562,7 +578,8 @@ class StageEngine:
         net = self._net(o.kind == OpKind.T)
         meta = self.meta.fetch(f"f{self.topo.stage - 1}", net, o.batch)
         self.fwd_posted[(o.kind, o.batch, o.view, o.ub)] = [
-            (self.fwd_in.post_recv(specs), tree, wrapped, others) for specs, tree, wrapped, others in meta]
+            (self.fwd_in.post_recv([(sh, dt) for sh, dt, _ in specs]), tree, wrapped, others,
+             [rg for _, _, rg in specs]) for specs, tree, wrapped, others in meta]
 
     # -- forward -------------------------------------------------------------------------------------
     def _forward(self, op: Op, teacher: bool) -> None:
@@ -572,16 +589,18 @@ class StageEngine:
         with self._on_compute(), self._prof("compute", op, teacher):
             if first:
                 data = self._stage0_input(op, teacher)
-                pieces = [data] if n_piece == 1 else pt.generic_scatter(data, n_piece)
+                pieces = [(d, None) for d in ([data] if n_piece == 1 else pt.generic_scatter(data, n_piece))]
             else:
                 pieces = self._recv_forward(op, teacher)
             outs, stored_in, stored_out = [], [], []
             gin_idx: List[int] = []
             gout_idx: List[int] = []
-            for x in pieces:
+            for x, flags in pieces:
                 leaves, tree, wrapped = pt.flatten(x)
                 if not teacher and not first:
-                    gin_idx = [i for i, l in enumerate(leaves) if isinstance(l, torch.Tensor) and l.is_floating_point()]
+                    # the sender says which tensor leaves carry a gradient back (same order as the tensors)
+                    tensor_pos = [i for i, l in enumerate(leaves) if isinstance(l, torch.Tensor)]
+                    gin_idx = [i for i, rg in zip(tensor_pos, flags) if rg]
                     for i in gin_idx:
                         leaves[i] = leaves[i].detach().requires_grad_(True)
                     x = pt.unflatten(leaves, tree, wrapped)
@@ -618,7 +637,8 @@ class StageEngine:
             leaves, tree, wrapped = pt.flatten(y)
             ts = [l.detach() for l in leaves if isinstance(l, torch.Tensor)]
             others = [(i, l) for i, l in enumerate(leaves) if not isinstance(l, torch.Tensor)]
-            meta.append(([(tuple(t.shape), t.dtype) for t in ts], tree, wrapped, others))
+            rgs = [bool(l.requires_grad and l.dim() > 0) for l in leaves if isinstance(l, torch.Tensor)]
+            meta.append(([(tuple(t.shape), t.dtype, rg) for t, rg in zip(ts, rgs)], tree, wrapped, others))
             tensors.append(ts)
         self.meta.publish(f"f{self.topo.stage}", net, op.batch, meta)
         for ts in tensors:

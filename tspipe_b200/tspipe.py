@@ -254,6 +254,12 @@ class TSPipe:
         bal_tg = split["target"] or default_balance(len(self.module_target), pp)
         self.partitions_online, self.partitions_target = split_module(
             self.module_online, self.module_target, self.module_predictor, bal_on, bal_tg)
+        from .skip import Skippable, verify_skippables, wrap_partitions
+        for parts in (self.partitions_online, self.partitions_target):
+            if any(isinstance(m, Skippable) for p_ in parts for m in p_.children()):
+                verify_skippables(nn.Sequential(*[m for p_ in parts for m in p_.children()]))
+        self.partitions_online = wrap_partitions(self.partitions_online)
+        self.partitions_target = wrap_partitions(self.partitions_target)
         self.ema_plans = None
         if getattr(self.target_update_fn, "is_ema", False):
             from .runtime.ema_plan import build_ema_plans
