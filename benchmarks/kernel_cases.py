@@ -1,0 +1,123 @@
+"""Small stand-alone cases of the hand-written kernels, for profiling one kernel at a time.
+
+    python benchmarks/kernel_cases.py bn        # fused BatchNorm fwd/bwd on one ResNet-50 activation
+    python benchmarks/kernel_cases.py lars      # flat LARS + fused EMA step over 25 M parameters
+    python benchmarks/kernel_cases.py ema       # momentum-teacher update over 25 M parameters
+    python benchmarks/kernel_cases.py kd        # soft-target KD loss on [2048, 1000] logits
+    python benchmarks/kernel_cases.py ln        # LayerNorm fwd/bwd on [512*197, 768]
+    python benchmarks/kernel_cases.py gemm      # tcgen05 GEMM 8192 x 3072 x 768
+
+Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2 where DRAM figures
+matter), runs the op a handful of times and prints CUDA-event timings with the achieved bandwidth.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def _time(fn, n=5, flush=None):
+    fn()
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(n):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best * 1e3
+
+
+def case_bn():
+    from tspipe_b200.batchnorm import DeferredBatchNorm
+    from tspipe_b200.ops import bn as fbn
+    dev = torch.device("cuda")
+    shp = (128, 64, 112, 112)
+    x = torch.randn(shp, device=dev).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+    g = torch.randn(shp, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+    bn = DeferredBatchNorm(64, chunks=10 ** 9).to(dev)
+    nbytes = x.numel() * 2
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tf = _time(lambda: fbn.bn_act(bn, x, None, True), flush=flush)
+    y = fbn.bn_act(bn, x, None, True)
+    tb = _time(lambda: torch.autograd.grad(y, x, g, retain_graph=True), flush=flush)
+    print(f"bn fwd  {shp}: {tf:8.1f} us  {3 * nbytes / tf / 1e6:5.2f} TB/s (read x twice, write y)")
+    print(f"bn bwd  {shp}: {tb:8.1f} us  {5 * nbytes / tb / 1e6:5.2f} TB/s (read dy,x twice, write dx)")
+
+
+def case_lars():
+    from tspipe_b200.optim import LARS
+    from tspipe_b200.runtime.state import FlatParams
+    dev = torch.device("cuda")
+    ps = [torch.nn.Parameter(torch.randn(2048, 1024, device=dev)) for _ in range(12)] + \
+         [torch.nn.Parameter(torch.randn(2048, device=dev)) for _ in range(12)]
+    flat = FlatParams(ps, dev, with_grad=True)
+    flat.grad.normal_()
+    opt = LARS(ps, lr=0.1, weight_decay=1e-6)
+    opt.bind_flat(flat, use_kernel=True)
+    opt.teacher_flat, opt.ema_momentum = torch.randn(flat.total, device=dev), 0.996
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    t = _time(opt.step, flush=flush)
+    n = flat.total
+    print(f"lars+ema step over {n / 1e6:.1f} M params: {t:8.1f} us  {n * 4 * 9 / t / 1e6:5.2f} TB/s "
+          "(norms: read p,g; apply: read p,g,mu,t write p,mu,t)")
+
+
+def case_ema():
+    from tspipe_b200.ops import fused
+    dev = torch.device("cuda")
+    n = 64 << 20
+    t_, s_ = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    t = _time(lambda: fused.ema_update_(t_, s_, 0.996), flush=flush)
+    print(f"ema over {n / 1e6:.0f} M params: {t:8.1f} us  {n * 12 / t / 1e6:5.2f} TB/s")
+
+
+def case_kd():
+    from tspipe_b200.ops import fused
+    dev = torch.device("cuda")
+    s = torch.randn(2048, 1000, device=dev).bfloat16().requires_grad_()
+    tt = torch.randn(2048, 1000, device=dev).bfloat16()
+    y = torch.randint(0, 1000, (2048,), device=dev)
+    t = _time(lambda: fused.kd_soft_target_loss(s, tt, y, 4.0, 0.9))
+    print(f"kd loss [2048,1000] fwd+grad: {t:8.1f} us")
+
+
+def case_ln():
+    from tspipe_b200.ops import fused
+    dev = torch.device("cuda")
+    rows, d = 512 * 197, 768
+    x = torch.randn(rows, d, device=dev).bfloat16().requires_grad_()
+    w = torch.ones(d, device=dev, requires_grad=True)
+    b = torch.zeros(d, device=dev, requires_grad=True)
+    g = torch.randn(rows, d, device=dev).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tf = _time(lambda: fused.layer_norm(x, w, b, 1e-6), flush=flush)
+    y = fused.layer_norm(x, w, b, 1e-6)
+    tb = _time(lambda: torch.autograd.grad(y, (x, w, b), g, retain_graph=True), flush=flush)
+    nb = rows * d * 2
+    print(f"layernorm fwd [{rows},{d}]: {tf:8.1f} us  {2 * nb / tf / 1e6:5.2f} TB/s")
+    print(f"layernorm bwd [{rows},{d}]: {tb:8.1f} us  {3 * nb / tb / 1e6:5.2f} TB/s")
+
+
+def case_gemm():
+    from tspipe_b200.ops import gemm
+    dev = torch.device("cuda")
+    m, n, k = 8192, 3072, 768
+    a = torch.randn(m, k, device=dev).bfloat16()
+    b = torch.randn(n, k, device=dev).bfloat16()
+    t = _time(lambda: gemm.matmul_nt(a, b), n=10)
+    tr = _time(lambda: a @ b.t(), n=10)
+    print(f"tcgen05 gemm {m}x{n}x{k}: {t:8.1f} us  {2 * m * n * k / t / 1e6:7.1f} TFLOP/s   (library: {tr:8.1f} us)")
+
+
+if __name__ == "__main__":
+    {"bn": case_bn, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm}[sys.argv[1]]()

@@ -66,32 +66,34 @@ __global__ void __launch_bounds__(kBlock) bn_colsum_kernel(const T* __restrict__
     }
   }
   if (active) {
-    const int64_t step = (int64_t)gridDim.x * tl.ty_n;
+    // each block owns one contiguous range of rows: consecutive iterations stream consecutive memory
+    const int64_t rows_per_block = (m + gridDim.x - 1) / gridDim.x;
+    const int64_t r_begin = (int64_t)blockIdx.x * rows_per_block;
+    const int64_t r_end = r_begin + rows_per_block < m ? r_begin + rows_per_block : m;
+    const int64_t step = tl.ty_n;
     const int64_t col = (int64_t)cg * 8;
-    int64_t r = (int64_t)blockIdx.x * tl.ty_n + ty;
+    int64_t r = r_begin + ty;
     if (MODE == 0) {
-      // four independent 16-byte loads in flight per thread
-      for (; r + 3 * step < m; r += 4 * step) {
-        float v0[8], v1[8], v2[8], v3[8];
-        tsp::ld8(x, r * c + col, v0);
-        tsp::ld8(x, (r + step) * c + col, v1);
-        tsp::ld8(x, (r + 2 * step) * c + col, v2);
-        tsp::ld8(x, (r + 3 * step) * c + col, v3);
+      // eight independent 16/32-byte loads in flight per thread before any arithmetic
+      for (; r + 7 * step < r_end; r += 8 * step) {
+        float v[8][8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          a[e] += (v0[e] + v1[e]) + (v2[e] + v3[e]);
-          b[e] += (v0[e] * v0[e] + v1[e] * v1[e]) + (v2[e] * v2[e] + v3[e] * v3[e]);
+        for (int u = 0; u < 8; ++u) tsp::ld8(x, (r + u * step) * c + col, v[u]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { a[e] += v[u][e]; b[e] += v[u][e] * v[u][e]; }
         }
       }
-      for (; r < m; r += step) {
+      for (; r < r_end; r += step) {
         float v0[8];
         tsp::ld8(x, r * c + col, v0);
 #pragma unroll
         for (int e = 0; e < 8; ++e) { a[e] += v0[e]; b[e] += v0[e] * v0[e]; }
       }
     } else {
-      for (; r < m; r += 2 * step) {
-        const bool two = r + step < m;
+      for (; r < r_end; r += 2 * step) {
+        const bool two = r + step < r_end;
         const int64_t off0 = r * c + col, off1 = (r + step) * c + col;
         float x0[8], x1[8], g0[8], g1[8], y0[8], y1[8];
         tsp::ld8(x, off0, x0);
@@ -157,7 +159,8 @@ __global__ void __launch_bounds__(kBlock) bn_apply_kernel(const T* __restrict__ 
                                                           const float* __restrict__ w, const float* __restrict__ b,
                                                           float* __restrict__ save_mean_rstd,
                                                           float* __restrict__ acc_sum, float* __restrict__ acc_sumsq,
-                                                          int64_t m, int c, float eps, int relu) {
+                                                          float* __restrict__ acc_count, int64_t m, int c, float eps,
+                                                          int relu) {
   extern __shared__ float sm[];
   float* scale = sm;
   float* shift = sm + c;
@@ -172,6 +175,7 @@ __global__ void __launch_bounds__(kBlock) bn_apply_kernel(const T* __restrict__ 
       var = fmaxf(q * inv_m - mean * mean, 0.f);
       if (blockIdx.x == 0) {
         if (acc_sum != nullptr) { acc_sum[i] += s; acc_sumsq[i] += q; }
+        if (acc_count != nullptr) acc_count[i] += (float)m;
       }
     }
     const float rstd = rsqrtf(var + eps);
@@ -329,8 +333,8 @@ int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaSt
 }
 
 int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
-                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq, int64_t m,
-                 int c, float eps, int relu, int dtype, cudaStream_t stream) {
+                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq,
+                 float* acc_count, int64_t m, int c, float eps, int relu, int dtype, cudaStream_t stream) {
   if (m <= 0) return 0;
   if (c % 8 != 0 || c > 4096) return -3;
   const size_t smem = sizeof(float) * 2 * (size_t)c;
@@ -338,11 +342,12 @@ int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, con
   if (dtype == TSP_DTYPE_BF16)
     bn_apply_kernel<__nv_bfloat16><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
                                                                    (__nv_bfloat16*)y, sums, fixed_mean_var, w, b,
-                                                                   save_mean_rstd, acc_sum, acc_sumsq, m, c, eps, relu);
+                                                                   save_mean_rstd, acc_sum, acc_sumsq, acc_count, m, c, eps,
+                                                                   relu);
   else
     bn_apply_kernel<float><<<grid, kBlock, smem, stream>>>((const float*)x, (const float*)res, (float*)y, sums,
-                                                           fixed_mean_var, w, b, save_mean_rstd, acc_sum, acc_sumsq, m,
-                                                           c, eps, relu);
+                                                           fixed_mean_var, w, b, save_mean_rstd, acc_sum, acc_sumsq,
+                                                           acc_count, m, c, eps, relu);
   return TSP_LAUNCH_CHECK();
 }
 

@@ -1,0 +1,317 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[N,K]^T (+ bias) (-> GELU), fp32 accumulation.
+//
+//   * operands staged by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, each CTA loads its own tiles) into a 4-stage
+//     shared-memory ring, one elected producer thread;
+//   * tcgen05.mma.cta_group::1.kind::f16 (UMMA 128 x BN x 16) issued by one elected thread, accumulators in
+//     tensor memory (TMEM), smem slots released with tcgen05.commit -> mbarrier;
+//   * four epilogue warps read the accumulator with tcgen05.ld (32 lanes x 32 columns per instruction), fuse
+//     bias / GELU, convert and store 16-byte vectors.
+// Reference call sites: every nn.Linear of the ViT / BERT blocks and heads (library GEMMs there:
+// `benchmarks/moco-v3/vits.py`, `benchmarks/distilbert/bert.py`, `benchmarks/byol/models/mlp_head.py`).
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiting role records an error code in
+// `status[0]`, stops issuing work and the CTA runs to its normal end (TMEM is released, nothing traps).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tspipe_kernels.h"
+
+namespace {
+
+constexpr int BM = 128;          // CTA tile rows  (UMMA M)
+constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;    // warp 0: TMA, warp 1: MMA + TMEM alloc, warps 2..5: epilogue
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait.  Returns false (and leaves an error code) when the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*((volatile int*)status) != 0) return false;      // another role already gave up
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                              // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: D = f32, A = B = bf16, both K-major, dense.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+template <int BN>
+struct Cfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = BN;                 // power of two >= 32
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// epilogue modes
+constexpr int EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2;
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
+                    int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  using C = Cfg<BN>;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(tiles + kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                 // [kStages]
+  uint64_t* empty_bar = bars + kStages;      // [kStages]
+  uint64_t* tmem_full_bar = bars + 2 * kStages;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + s, 1);
+      mbar_init(empty_bar + s, 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+  }
+  if (warp == 1) {        // one full warp allocates the accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t round = kb / kStages;
+        if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1)) break;
+        uint8_t* a_dst = tiles + s * C::kStageBytes;
+        uint8_t* b_dst = a_dst + C::kABytes;
+        mbar_expect_tx(full_bar + s, (uint32_t)C::kStageBytes);
+        tma_load_2d(a_dst, &tmap_a, full_bar + s, kb * BK, m0);
+        tma_load_2d(b_dst, &tmap_b, full_bar + s, kb * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t round = kb / kStages;
+        ok = mbar_wait(full_bar + s, round & 1, status, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
+        const uint32_t b_addr = a_addr + C::kABytes;
+        const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(b_addr);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+          umma_bf16(tmem_base, a_desc + (uint64_t)(2 * kk), b_desc + (uint64_t)(2 * kk), idesc,
+                    (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar + s);          // smem slot is free once these MMAs have read it
+      }
+      umma_commit(tmem_full_bar);            // accumulator complete (or: nothing more will be issued)
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lanes 32*(warp%4) .. +31 ----------------
+    const int quarter = warp & 3;
+    const bool ok = mbar_wait(tmem_full_bar, 0, status, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int row = m0 + quarter * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        const int col = n0 + c0;
+        if (row < m && col < n) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (epi != EPI_NONE) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float bj = (col + j < n) ? bias[col + j] : 0.f;
+              v[j] += bj;
+              if (epi == EPI_BIAS_GELU) v[j] = gelu_erf(v[j]);
+            }
+          }
+          OutT* dst = c + (int64_t)row * ldc + col;
+          if (col + 32 <= n && ((ldc * (int)sizeof(OutT)) % 16 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float t8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) t8[e] = v[j + e];
+              tsp::st8(dst, j, t8);
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < n; ++j) tsp::st(dst, j, v[j]);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)C::kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side: tensor maps through the driver entry point (no link-time dependency on libcuda)
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] tensor, box = [box_rows, 64 columns], 128-byte swizzle, zero fill out of bounds
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, typename OutT>
+int launch(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
+           int epi, int* status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (!make_map(&ta, a, m, k, lda, BM) || !make_map(&tb, b, n, k, ldb, BN)) return -6;
+  auto kern = gemm_tcgen05_kernel<BN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, (OutT*)c, bias, m, n, k, ldc, epi, status);
+  return TSP_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+extern "C" {
+
+// C[m,n] = A[m,k] * B[n,k]^T (+ bias[n]) (-> GELU).  A, B bf16 row-major with leading dimensions lda / ldb
+// (elements; multiples of 8, base pointers 16-byte aligned); C bf16 (out_dtype 1) or fp32 (0), leading dim ldc.
+// epi: 0 none, 1 bias, 2 bias + GELU.  `status` is one int in device memory, zeroed by the caller; a non-zero
+// value after the kernel means a bounded wait ran out (1 producer, 2 MMA, 3 epilogue) and C is not valid.
+int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,
+                     int ldc, int out_dtype, int epi, int* status, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (k % 8)) return -3;
+  if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
+  if (epi != 0 && bias == nullptr) return -3;
+  const bool wide = n >= 256;
+  if (out_dtype == TSP_DTYPE_BF16)
+    return wide ? launch<256, __nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
+                : launch<128, __nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+  return wide ? launch<256, float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
+              : launch<128, float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+}
+
+}  // extern "C"

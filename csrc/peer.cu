@@ -132,6 +132,17 @@ __global__ void __launch_bounds__(kThreads) dp_adamw_kernel(PeerPtrs grads, Peer
   }
 }
 
+// dst[r * n + i] = src_r[i]: concatenate one equally sized block per peer (16-byte units) into local memory.
+__global__ void __launch_bounds__(kThreads) gather_blocks_kernel(PeerPtrs srcs, int n_peers, int64_t n16,
+                                                                 uint4* __restrict__ dst) {
+  const int64_t total = n16 * n_peers;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n16);
+    const int64_t j = i - (int64_t)r * n16;
+    dst[i] = reinterpret_cast<const uint4*>(srcs.p[r])[j];
+  }
+}
+
 inline bool fill(PeerPtrs& dst, void* const* src, int n) {
   if (n < 1 || n > kMaxPeers) return false;
   for (int i = 0; i < kMaxPeers; ++i) dst.p[i] = i < n ? (float*)src[i] : nullptr;
@@ -178,6 +189,19 @@ int tsp_ipc_import(const unsigned char* handle64, void** base) {
 }
 
 int tsp_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }
+
+// All-gather by peer loads: block r of `dst` receives `bytes_each` bytes read from srcs[r] (own or peer memory).
+int tsp_gather_blocks(void* const* srcs, int n_peers, int64_t bytes_each, void* dst, cudaStream_t stream) {
+  if (bytes_each <= 0) return 0;
+  if (bytes_each % 16) return -3;
+  PeerPtrs sp;
+  if (!fill(sp, srcs, n_peers)) return -3;
+  const int64_t n16 = bytes_each / 16;
+  int64_t blocks = (n16 * n_peers + kThreads - 1) / kThreads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  gather_blocks_kernel<<<(int)blocks, kThreads, 0, stream>>>(sp, n_peers, n16, (uint4*)dst);
+  return TSP_LAUNCH_CHECK();
+}
 
 int tsp_dp_reduce_norms(void* const* grads, int n_peers, float scale, float* g_out, const float* p,
                         const int64_t* chunks, int n_chunks, const float* seg_hp, float* norms, int n_seg,

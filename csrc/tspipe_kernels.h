@@ -48,8 +48,8 @@ int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int
 // ---- batchnorm.cu -----------------------------------------------------------------------------------------------
 int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
 int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
-                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq, int64_t m,
-                 int c, float eps, int relu, int dtype, cudaStream_t stream);
+                 const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq,
+                 float* acc_count, int64_t m, int c, float eps, int relu, int dtype, cudaStream_t stream);
 int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, const float* mean_rstd, const float* w,
                       const float* bias, int relu, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
 int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean_rstd, const float* w,
@@ -60,6 +60,7 @@ int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* 
 int tsp_enable_peer_access(int peer_device);
 int tsp_ipc_import(const unsigned char* handle64, void** base);
 int tsp_ipc_close(void* base);
+int tsp_gather_blocks(void* const* srcs, int n_peers, int64_t bytes_each, void* dst, cudaStream_t stream);
 int tsp_dp_reduce_norms(void* const* grads, int n_peers, float scale, float* g_out, const float* p,
                         const int64_t* chunks, int n_chunks, const float* seg_hp, float* norms, int n_seg,
                         cudaStream_t stream);
@@ -67,6 +68,10 @@ int tsp_dp_lars_apply(void* const* params, int n_peers, int self, const float* g
                       int n_chunks, const float* seg_hp, const float* norms, cudaStream_t stream);
 int tsp_dp_adamw_step(void* const* grads, void* const* params, int n_peers, int self, float scale, float* m, float* v,
                       const int64_t* chunks, int n_chunks, const float* seg_hp, cudaStream_t stream);
+
+// ---- gemm_tcgen05.cu ------------------------------------------------------------------------------------------
+int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,
+                     int ldc, int out_dtype, int epi, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

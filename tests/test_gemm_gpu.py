@@ -1,0 +1,65 @@
+"""tcgen05 / TMEM / TMA GEMM against an fp32 PyTorch product of the same bf16-rounded operands."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (200, 136, 72), (1024, 768, 768),
+                                   (4096, 4096, 256)])
+def test_matmul_nt_matches_fp32_reference(m, n, k):
+    from tspipe_b200.ops import gemm
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    a = torch.randn(m, k, device=dev).bfloat16()
+    b = torch.randn(n, k, device=dev).bfloat16()
+    c = gemm.matmul_nt(a, b, out_dtype=torch.float32)
+    gemm.check_status()
+    ref = a.float() @ b.float().t()
+    torch.testing.assert_close(c, ref, rtol=1e-3, atol=1e-2 * (k ** 0.5) / 8)
+    c16 = gemm.matmul_nt(a, b)
+    gemm.check_status()
+    torch.testing.assert_close(c16.float(), ref, rtol=2e-2, atol=0.1 * (k ** 0.5) / 8)
+
+
+def test_bias_gelu_epilogue():
+    from tspipe_b200.ops import gemm
+    torch.manual_seed(1)
+    dev = torch.device("cuda", 0)
+    a = (torch.randn(512, 256, device=dev) * 0.5).bfloat16()
+    b = (torch.randn(384, 256, device=dev) * 0.1).bfloat16()
+    bias = torch.randn(384, device=dev)
+    y = gemm.matmul_nt(a, b, bias, gelu=True, out_dtype=torch.float32)
+    gemm.check_status()
+    ref = F.gelu(a.float() @ b.float().t() + bias)
+    torch.testing.assert_close(y, ref, rtol=1e-3, atol=1e-3)
+
+
+def test_linear_autograd_and_info_nce():
+    from tspipe_b200.ops import fused, gemm
+    torch.manual_seed(2)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(4, 64, 128, device=dev, requires_grad=True)
+    w = (torch.randn(256, 128, device=dev) * 0.1).requires_grad_()
+    bias = torch.randn(256, device=dev, requires_grad=True)
+    y = gemm.linear(x, w, bias)
+    y.float().pow(2).mean().backward()
+    gemm.check_status()
+    xr, wr, br = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_(), bias.detach().clone().requires_grad_()
+    yr = F.linear(xr, wr, br)
+    yr.pow(2).mean().backward()
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(x.grad, xr.grad, rtol=5e-2, atol=2e-4)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=5e-2, atol=2e-4)
+    q = torch.randn(512, 256, device=dev, requires_grad=True)
+    k = torch.randn(512, 256, device=dev)
+    loss = fused.info_nce_loss(q, k, 0.2)
+    loss.backward()
+    gemm.check_status()
+    qr = q.detach().clone().requires_grad_()
+    logits = F.normalize(qr, dim=1) @ F.normalize(k, dim=1).t() / 0.2
+    ref = F.cross_entropy(logits, torch.arange(512, device=dev)) * 0.4
+    ref.backward()
+    torch.testing.assert_close(loss, ref.detach(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q.grad, qr.grad, rtol=1e-1, atol=2e-4)

@@ -142,3 +142,65 @@ def test_ssl_momentum_pipeline_matches_oracle(pp, n_ub, split, skip, gpipe):
     assert len(got_o) == len(want_o)
     for a, b in zip(got_o, want_o):
         torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+def _moco_models():
+    torch.manual_seed(3)
+    online = mlp_sequential([20, 32, 24, 16])
+    target = copy.deepcopy(online)
+    predictor = nn.Sequential(nn.Linear(16, 16), nn.Tanh(), nn.Linear(16, 16))
+    return online, target, predictor
+
+
+def _moco_batches(n):
+    g = torch.Generator().manual_seed(4)
+    return [(torch.randn(16, 20, generator=g), torch.randn(16, 20, generator=g)) for _ in range(n)]
+
+
+def _moco_rank(rank, world, cfg, n_steps):
+    from tspipe_b200.losses import moco_loss
+    online, target, predictor = _moco_models()
+    opt = torch.optim.SGD(list(online.parameters()) + list(predictor.parameters()), lr=0.2)
+    tsp = TSPipe(online, target, predictor, opt, moco_loss, ema_update, 0.9, "", config=cfg, device="cpu",
+                 extra_args=Namespace(moco_t=0.2))
+    dp = cfg["runtime"]["dp_replicas"]
+    rep = tsp.topo.replica
+    losses = []
+    for a, b in _moco_batches(n_steps):
+        per = a.shape[0] // dp
+        sl = slice(rep * per, (rep + 1) * per)
+        l = tsp.feed(a[sl], b[sl]) if tsp.topo.is_first else tsp.feed(None, None)
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    return losses, tsp.state_dicts()[0], (tsp.topo.replica, tsp.topo.stage)
+
+
+@pytest.mark.parametrize("pp,dp", [(1, 2), (2, 2)])
+def test_moco_data_parallel_replicas_gather_keys(pp, dp):
+    """MoCo-style InfoNCE with ``dp`` pipeline replicas: keys are all-gathered across replicas, gradients are
+    averaged, and the result equals single-process training on the full batch."""
+    from tspipe_b200.losses import moco_loss
+    from tspipe_b200.tspipe import default_balance
+    n_steps = 4
+    online, target, predictor = _moco_models()
+    full = nn.Sequential(*list(online.children()), *list(predictor.children()))
+    opt = torch.optim.SGD(full.parameters(), lr=0.2)
+    orc = DelayedTeacherOracle(full, target, opt, moco_loss, ema_update, 0.9, kd=False, n_ubatch=2 * dp, bwd_split=1,
+                               extra_args=Namespace(moco_t=0.2))
+    n_t = len(list(target.parameters()))
+    f = orc.update_fn
+    orc.update_fn = lambda m, on, tg: f(m, on[:n_t], tg)
+    ref = [orc.step(a, b) for a, b in _moco_batches(n_steps)]
+    cfg = {"model_split": {"online": default_balance(4 + 3, pp), "target": default_balance(4, pp)},
+           "runtime": {"num_ubatch": 2, "bwd_split": 1, "backend": "gloo", "dp_replicas": dp, "timeout_s": 60},
+           "train": {"deferred_batch_norm": False}}
+    out = run_ranks(_moco_rank, pp * dp, cfg, n_steps)
+    last = [o for o in out if o[2][1] == pp - 1]
+    mean = [sum(x) / dp for x in zip(*[o[0] for o in last])]
+    torch.testing.assert_close(torch.tensor(mean), torch.tensor(ref), rtol=2e-5, atol=1e-6)
+    got = [v for j in sorted(out[0][1]) for v in out[0][1][j].values()]
+    want = list(full.state_dict().values())
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b.detach(), rtol=2e-5, atol=1e-6)

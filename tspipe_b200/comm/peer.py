@@ -66,8 +66,16 @@ def _export(tensor: torch.Tensor):
     """(ipc handle bytes, byte offset of ``tensor`` inside the exported allocation)."""
     st = tensor.untyped_storage()
     info = st._share_cuda_()
-    handle, off_bytes = info[1], info[3]
-    return bytes(handle), int(off_bytes) + tensor.storage_offset() * tensor.element_size()
+    handle, off_bytes = bytes(info[1]), info[3]
+    if len(handle) == 66:
+        # recent allocators prefix the 64-byte cudaIpcMemHandle_t with a version byte and a kind byte
+        # ('c' = plain cudaMalloc block, 'e' = expandable segment, which legacy IPC cannot export)
+        if handle[1:2] != b"c":
+            raise RuntimeError("peer mapping needs cudaMalloc-backed allocations (expandable_segments must be off)")
+        handle = handle[2:]
+    if len(handle) != 64:
+        raise RuntimeError(f"unexpected CUDA IPC handle length {len(handle)}")
+    return handle, int(off_bytes) + tensor.storage_offset() * tensor.element_size()
 
 
 def _import(handle: bytes) -> int:

@@ -51,20 +51,65 @@ def byol_loss(online_view_1, online_view_2, target_view_1, target_view_2, args=N
     return loss.mean()
 
 
-def _info_nce(q: torch.Tensor, k: torch.Tensor, T: float) -> torch.Tensor:
+def _info_nce(q: torch.Tensor, k: torch.Tensor, T: float, label_offset: int = 0) -> torch.Tensor:
     q = F.normalize(q.float(), dim=1)
     k = F.normalize(k.float(), dim=1)
     logits = q @ k.t() / T
-    labels = torch.arange(logits.shape[0], device=logits.device)
+    labels = torch.arange(logits.shape[0], device=logits.device) + label_offset
     return F.cross_entropy(logits, labels) * (2 * T)
 
 
 def moco_loss(online_view_1, online_view_2, target_view_1, target_view_2, args=None, extra_args=None):
+    """Symmetric InfoNCE (`benchmarks/moco-v3/main.py:147-162`).  With data-parallel pipeline replicas the keys of
+    all replicas are gathered first and the positives sit at ``arange(n) + n * replica``
+    (`benchmarks/moco-v3/moco/builder.py:73-85`)."""
+    from .parallel.keys import gather_keys
     T = float(getattr(extra_args, "moco_t", 0.2))
+    k2, off = gather_keys(target_view_2)
+    k1, _ = gather_keys(target_view_1)
     if _fused_ok(online_view_1, target_view_2) and not getattr(extra_args, "no_fused", False):
+        from .ops import gemm
+        return gemm.info_nce(online_view_1, target_view_2, T, k2, off) + \
+            gemm.info_nce(online_view_2, target_view_1, T, k1, off)
+    return _info_nce(online_view_1, k2, T, off) + _info_nce(online_view_2, k1, T, off)
+
+
+def distil_loss(student_out, teacher_out, labels, args=None, extra_args=None, epoch: int = 0):
+    """DistilBERT objective (`benchmarks/distilbert/distiller.py:711-772`):
+    ``alpha_ce * T^2 * KL(softmax(t/T) || softmax(s/T))`` over the tokens selected by the attention mask
+    (batch-mean over selected tokens) ``+ alpha_mlm * CE(s, lm_labels)`` (mean over labelled tokens,
+    ``-100`` ignored) ``+ alpha_cos * (1 - cos(h_s, h_t))`` over the selected tokens.
+
+    ``student_out`` / ``teacher_out`` are ``(logits [B, L, V], last_hidden [B, L, H])``; ``labels`` is
+    ``(lm_labels [B, L], attention_mask [B, L])`` optionally followed by the two token counts as Python
+    ints (saves a device synchronisation)."""
+    s_logits, s_hidden = student_out
+    t_logits, t_hidden = teacher_out
+    lm_labels, attn = labels[0], labels[1]
+    T = float(getattr(extra_args, "temperature", 2.0))
+    a_ce = float(getattr(extra_args, "alpha_ce", 5.0))
+    a_mlm = float(getattr(extra_args, "alpha_mlm", 2.0))
+    a_cos = float(getattr(extra_args, "alpha_cos", 1.0))
+    sel = attn.to(torch.bool)
+    n_sel = int(labels[3]) if len(labels) > 3 else int(sel.sum())
+    n_lab = int(labels[2]) if len(labels) > 2 else int((lm_labels >= 0).sum())
+    n_sel, n_lab = max(n_sel, 1), max(n_lab, 1)
+    if _fused_ok(s_logits, t_logits) and not getattr(extra_args, "no_fused", False):
         from .ops import fused
-        return fused.info_nce_loss(online_view_1, target_view_2, T) + fused.info_nce_loss(online_view_2, target_view_1, T)
-    return _info_nce(online_view_1, target_view_2, T) + _info_nce(online_view_2, target_view_1, T)
+        loss = fused.kd_ce_loss(s_logits, t_logits, lm_labels, T, a_mlm / n_lab, a_ce / n_sel, row_mask=sel)
+        if a_cos > 0:
+            loss = loss + fused.cosine_embedding_loss(s_hidden, t_hidden, a_cos / n_sel, row_mask=sel)
+        return loss
+    v = s_logits.shape[-1]
+    s_sel = s_logits.float()[sel]
+    t_sel = t_logits.float()[sel]
+    loss = a_ce * F.kl_div(F.log_softmax(s_sel / T, dim=-1), F.softmax(t_sel / T, dim=-1),
+                           reduction="batchmean") * T * T
+    loss = loss + a_mlm * F.cross_entropy(s_logits.float().view(-1, v), lm_labels.view(-1), ignore_index=-100)
+    if a_cos > 0:
+        hs, ht = s_hidden.float()[sel], t_hidden.float()[sel]
+        loss = loss + a_cos * F.cosine_embedding_loss(hs, ht, torch.ones(hs.shape[0], device=hs.device))
+    return loss
 
 
 @torch.no_grad()

@@ -61,7 +61,7 @@ def _lib():
 
 class _BnAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq):
+    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None):
         m, c = _as_rows(x)
         dt = _f._dt(x)
         L = _lib()
@@ -82,7 +82,7 @@ class _BnAct(torch.autograd.Function):
                 _f._count(2)
             _f._check(L.tsp_bn_apply(_f._ptr(x), _f._ptr(residual), _f._ptr(y), _f._ptr(sums), _f._ptr(fixed),
                                      _f._ptr(wf), _f._ptr(bf), _f._ptr(save), _f._ptr(acc_sum), _f._ptr(acc_sumsq),
-                                     _c.c_int64(m), _c.c_int(c), _c.c_float(eps), _c.c_int(1 if relu else 0),
+                                     _f._ptr(acc_count), _c.c_int64(m), _c.c_int(c), _c.c_float(eps), _c.c_int(1 if relu else 0),
                                      _c.c_int(dt), st), "tsp_bn_apply")
             _f._count()
         ctx.save_for_backward(x, y if (relu and residual is not None) else None, save, wf, bf)
@@ -126,7 +126,7 @@ class _BnAct(torch.autograd.Function):
             gres = dres if dres is not None else dy
         else:
             gres = None
-        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None
+        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None, None
 
 
 def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = False) -> torch.Tensor:
@@ -143,6 +143,10 @@ def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: b
     if not bn.training or not bn.track_running_stats and False:
         fixed = torch.cat([bn.running_mean.float(), bn.running_var.float()])
         y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, fixed, None, None)
+        return y
+    if isinstance(bn, DeferredBatchNorm) and bn.group is not None:
+        # the partition's statistics live in flat buffers; the group commits them (one launch set per mini-batch)
+        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, bn.count)
         return y
     if isinstance(bn, DeferredBatchNorm):
         y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares)

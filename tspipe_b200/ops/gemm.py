@@ -1,0 +1,131 @@
+"""Bindings of the tcgen05 / TMEM / TMA GEMM (``csrc/gemm_tcgen05.cu``) and the ops built on it.
+
+``matmul_nt(a, b)`` computes ``a @ b.T`` for row-major bf16 ``a [M, K]`` and ``b [N, K]`` with fp32
+accumulation in tensor memory, optional fused ``+ bias`` and GELU epilogue.  ``linear`` is the autograd
+wrapper used by the transformer blocks (forward on the tcgen05 kernel; the two backward products need
+transposed operands and use the library GEMM).  ``info_nce`` is the MoCo-v3 contrastive loss
+(`benchmarks/moco-v3/main.py:147-162`): row-normalised ``q @ k.T / T`` on the tcgen05 kernel followed
+by the fused cross-entropy kernel (value + gradient in one launch).
+
+The kernel bounds every barrier wait; a non-zero device status word after a launch means a wait ran
+out and the output is invalid - :func:`check_status` raises in that case.
+"""
+from __future__ import annotations
+
+import ctypes as _c
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import fused as _f
+
+_status = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    key = (device.type, device.index)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the GEMM status word (tests and debugging)."""
+    for key, t in _status.items():
+        code = int(t.item())
+        if code != 0:
+            t.zero_()
+            raise RuntimeError(f"tcgen05 GEMM on {key}: bounded wait ran out in role {code} "
+                               "(1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
+
+
+def eligible(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    k = x.shape[-1]
+    return (x.is_cuda and weight.is_cuda and k % 8 == 0 and k >= 64 and weight.shape[0] >= 64
+            and x.numel() // k >= 128)
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T`` (bf16 operands)."""
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
+    a = a if (a.dtype == torch.bfloat16 and a.is_contiguous()) else a.to(torch.bfloat16).contiguous()
+    b = b if (b.dtype == torch.bfloat16 and b.is_contiguous()) else b.to(torch.bfloat16).contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    c = torch.empty(m, n, dtype=out_dtype, device=a.device)
+    bf = None if bias is None else bias.detach().float().contiguous()
+    epi = 0 if bias is None else (2 if gelu else 1)
+    if gelu and bias is None:
+        bf, epi = torch.zeros(n, dtype=torch.float32, device=a.device), 2
+    L = _f.lib()
+    L.tsp_gemm_bf16_tn.restype = _c.c_int
+    with torch.cuda.device(a.device):
+        code = L.tsp_gemm_bf16_tn(_f._ptr(a), _f._ptr(b), _f._ptr(c), _f._ptr(bf), _c.c_int(m), _c.c_int(n), _c.c_int(k),
+                                  _c.c_int(k), _c.c_int(k), _c.c_int(n), _c.c_int(_f._dt(c)), _c.c_int(epi),
+                                  _f._ptr(_status_word(a.device)), _f._stream())
+    _f._check(code, "tsp_gemm_bf16_tn")
+    _f._count()
+    return c
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = matmul_nt(x2, weight, bias)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = x.shape
+        ctx.dtypes = (x.dtype, weight.dtype, None if bias is None else bias.dtype)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
+        dx = (dy2 @ weight.to(torch.bfloat16)).view(ctx.in_shape).to(ctx.dtypes[0])
+        dw = (dy2.t() @ x2.to(torch.bfloat16)).to(ctx.dtypes[1])
+        db = dy2.float().sum(0).to(ctx.dtypes[2]) if ctx.has_bias else None
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _Linear.apply(x, weight, bias)
+
+
+def info_nce(q: torch.Tensor, k: torch.Tensor, temp: float, k_all: Optional[torch.Tensor] = None,
+             label_offset: int = 0) -> torch.Tensor:
+    """``CE(normalize(q) @ normalize(k_all)^T / T, arange(N) + label_offset) * 2T``.  ``k_all`` defaults to
+    ``k`` (single replica); with data-parallel replicas it is the concatenation of every replica's keys
+    (gathered through peer memory, :func:`tspipe_b200.parallel.keys.gather_keys`)."""
+    keys = k if k_all is None else k_all
+    qn = F.normalize(q.float(), dim=1)
+    kn = F.normalize(keys.detach().float(), dim=1)
+    n = q.shape[0]
+    if q.is_cuda and q.shape[1] % 8 == 0 and q.shape[1] >= 64 and n >= 128 and keys.shape[0] >= 64:
+        logits = _ScaledLogits.apply(qn, kn, 1.0 / temp)
+    else:
+        logits = qn @ kn.t() / temp
+    labels = torch.arange(n, device=q.device) + label_offset
+    if q.is_cuda:
+        return _f.cross_entropy(logits, labels) * (2 * temp)
+    return F.cross_entropy(logits, labels) * (2 * temp)
+
+
+class _ScaledLogits(torch.autograd.Function):
+    """``scale * a @ b^T`` in fp32 on the tcgen05 kernel; gradient w.r.t. ``a`` only."""
+
+    @staticmethod
+    def forward(ctx, a, b, scale):
+        bb = (b * scale).to(torch.bfloat16)
+        ctx.save_for_backward(bb)
+        ctx.adtype = a.dtype
+        return matmul_nt(a.to(torch.bfloat16), bb, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, g):
+        (bb,) = ctx.saved_tensors
+        # dA = g @ (scale*b): [N, M] x [M, D] -> operands as (g, (scale*b)^T) for the TN kernel
+        return matmul_nt(g, bb.t().contiguous(), out_dtype=torch.float32).to(ctx.adtype), None, None

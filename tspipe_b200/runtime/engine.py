@@ -246,6 +246,9 @@ class StageEngine:
         self.target.train(target_train_mode)
         for p in self.target.parameters():
             p.requires_grad_(False)
+        from ..batchnorm import BatchNormGroup
+        self.bn_group_online = BatchNormGroup(self.online)
+        self.bn_group_target = BatchNormGroup(self.target)
 
         # flat state ---------------------------------------------------------------------------
         self.flat_online = FlatParams([p for p in self.online.parameters()], self.device, with_grad=True,
@@ -290,6 +293,7 @@ class StageEngine:
         self._flushing = False
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
+        self._amp_open = False
         self.error: Optional[BaseException] = None
         self.thread: Optional[threading.Thread] = None
         self.losses: "queue.Queue[Tuple[int, Any]]" = queue.Queue()
@@ -362,6 +366,8 @@ class StageEngine:
         return torch.cuda.stream(self.compute) if self.cuda else contextlib.nullcontext()
 
     def _amp(self):
+        if self._amp_open:
+            return contextlib.nullcontext()
         if self.autocast:
             return torch.autocast(device_type=self.device.type, dtype=torch.bfloat16)
         return contextlib.nullcontext()
@@ -384,6 +390,16 @@ class StageEngine:
 
     def _run_guarded(self) -> None:
         try:
+            if self.autocast and self.cuda:
+                # One autocast region for the executor's whole life: the bf16 copies of the weights are
+                # then cast once per optimizer step (the cache is dropped in _optimize) instead of once per
+                # microbatch forward.  Teacher weights take part in the cache only if they are flagged as
+                # requiring grad; they are only ever used under no_grad.
+                for p in self.target.parameters():
+                    p.requires_grad_(True)
+                self._amp_ctx = torch.autocast(device_type="cuda", dtype=torch.bfloat16)
+                self._amp_ctx.__enter__()
+                self._amp_open = True
             self.run()
         except BaseException as e:  # noqa: BLE001 - reported to the owner thread
             self.error = e
@@ -434,6 +450,9 @@ class StageEngine:
 
     # -- main loop ---------------------------------------------------------------------------------
     def run(self) -> None:
+        from . import context
+        context.set_current(context.RuntimeContext(self.topo, self.fused,
+                                                   bool(self.cfg["runtime"].get("peer_memory", True)) and self.cuda))
         b = 1
         while True:
             if not self._have_batch(b):
@@ -609,9 +628,11 @@ class StageEngine:
                 if teacher:
                     with torch.no_grad(), self._amp():
                         y = module(x)
+                    self.bn_group_target.step()
                 else:
                     with self._amp():
                         y = module(x)
+                    self.bn_group_online.step()
                 outs.append(y)
                 if not teacher:
                     oleaves = pt.flatten(y)[0]
@@ -777,6 +798,8 @@ class StageEngine:
                 self.optimizer.step()
             self.updater.step(self.momentum)
             self.flat_online.zero_grad()
+            if self._amp_open:
+                torch.clear_autocast_cache()
             self.steps_done += 1
 
     def _dp_sync(self) -> None:
