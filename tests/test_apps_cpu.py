@@ -1,0 +1,84 @@
+"""The training entry points under ``benchmarks/`` run end to end (tiny models, CPU, gloo)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from tests.helpers import free_port
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _write(tmp_path, name, text):
+    p = tmp_path / name
+    p.write_text(text)
+    return str(p)
+
+
+def _run(cmd, nproc=1, timeout=240):
+    env = dict(os.environ, TSPIPE_NO_AFFINITY="1", OMP_NUM_THREADS="1")
+    full = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+            "--master-addr", "127.0.0.1", "--master-port", str(free_port())] + cmd
+    res = subprocess.run(full, env=env, capture_output=True, text=True, timeout=timeout, cwd=REPO)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+def test_distilbert_app_two_stage_pipeline(tmp_path):
+    cfg = _write(tmp_path, "t.yaml", """
+tspipe:
+  train: {deferred_batch_norm: False}
+  model_split: {online: [2, 1], target: [2, 2]}
+  runtime: {num_ubatch: 2, bwd_split: 2, backend: gloo, timeout_s: 60}
+""")
+    out = _run(["benchmarks/distilbert/train.py", "--teacher", "tiny", "--batch-size", "8", "--seq-len", "16",
+                "--iters", "12", "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)], nproc=2)
+    assert "iter 10 loss" in out
+
+
+def test_soft_target_app_single_stage(tmp_path):
+    cfg = _write(tmp_path, "t.yaml", """
+tspipe:
+  train: {deferred_batch_norm: False}
+  model_split: {online: [8], target: [8]}
+  runtime: {num_ubatch: 2, bwd_split: 1, backend: gloo, timeout_s: 60}
+""")
+    out = _run(["benchmarks/soft_target/train_kd.py", "--t-name", "vit_tiny_test", "--s-name", "vit_tiny_test",
+                "--image", "32", "--num-class", "10", "--batch-size", "8", "--iters-per-epoch", "11",
+                "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)])
+    assert "iter 10 loss" in out
+
+
+def test_moco_app_with_replicas(tmp_path):
+    cfg = _write(tmp_path, "t.yaml", """
+tspipe:
+  train: {deferred_batch_norm: True}
+  model_split: {online: [20], target: [15]}
+  runtime: {num_ubatch: 2, bwd_split: 1, backend: gloo, dp_replicas: 2, timeout_s: 60}
+""")
+    out = _run(["benchmarks/moco_v3/main.py", "--arch", "vit_tiny_test", "--image", "32", "--batch-size", "8",
+                "--moco-dim", "32", "--moco-mlp-dim", "64", "--max-iters", "11", "--dummy",
+                "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)], nproc=2)
+    assert "iter 10 loss" in out
+
+
+def test_byol_app_two_stages(tmp_path):
+    cfg = _write(tmp_path, "t.yaml", """
+tspipe:
+  train: {deferred_batch_norm: True, save_model_every_iter: 5}
+  model_split: {online: [6, 16], target: [6, 12]}
+  runtime: {num_ubatch: 2, bwd_split: 2, backend: gloo, timeout_s: 60}
+""")
+    app = _write(tmp_path, "c.yaml", """
+network: {name: resnet18, projection_head: {mlp_hidden_size: 32, projection_size: 16}}
+data_transforms: {input_shape: "(32,32,3)"}
+dataset: {name: dummy, path: ""}
+trainer: {batch_size: 8, m: 0.99, max_epochs: 1, num_workers: 0, dummy_input: True, optimizer_type: lars}
+optimizer: {params: {lr: 0.1, momentum: 0.9, weight_decay: 0.000001}}
+""")
+    out = _run(["benchmarks/byol/main.py", "--config", app, "--tspipe-config", cfg, "--max-iters", "12",
+                "--artifact-dir", str(tmp_path)], nproc=2)
+    assert "iter 10 loss" in out
+    assert (tmp_path / "model_batch5_part0.pt").exists() and (tmp_path / "model_batch10_part1.pt").exists()
+    assert (tmp_path / "profile_out.csv").exists()

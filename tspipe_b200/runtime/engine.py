@@ -293,6 +293,7 @@ class StageEngine:
         self._flushing = False
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
+        self.watchdog = None
         self._amp_open = False
         self.error: Optional[BaseException] = None
         self.thread: Optional[threading.Thread] = None
@@ -378,7 +379,22 @@ class StageEngine:
         return self.profiler.operation(name, op.batch, op.view, op.ub, is_target, self.topo.stage)
 
     # -- feeder side -------------------------------------------------------------------------------
+    def start_watchdog(self) -> None:
+        from .watchdog import Watchdog
+        rt = self.cfg["runtime"]
+        if self.topo.world <= 1 or not rt.get("heartbeat_s"):
+            return
+        self.watchdog = Watchdog(self.topo.store, self.topo.rank, self.topo.world, rt["heartbeat_s"], rt["timeout_s"],
+                                 progress=lambda: self.op_count, on_failure=self._peer_failed)
+        self.watchdog.start()
+
+    def _peer_failed(self, exc: BaseException) -> None:
+        if self.error is None:
+            self.error = exc
+            self.losses.put((-1, exc))
+
     def start(self) -> None:
+        self.start_watchdog()
         self.thread = threading.Thread(target=self._run_guarded, name=f"tspipe-exec-{self.topo.rank}", daemon=True)
         self.thread.start()
 
@@ -402,13 +418,19 @@ class StageEngine:
                 self._amp_open = True
             self.run()
         except BaseException as e:  # noqa: BLE001 - reported to the owner thread
-            self.error = e
+            first = self.error is None
+            if first:
+                self.error = e
             Log.e(f"rank {self.topo.rank} executor died:\n{traceback.format_exc()}")
             self.losses.put((-1, e))
-            try:
-                self.topo.store.set(f"dead/{self.topo.rank}", repr(e))
-            except Exception:
-                pass
+            if first:
+                try:
+                    self.topo.store.set(f"dead/{self.topo.rank}", repr(e).encode()[:2000])
+                except Exception:
+                    pass
+        finally:
+            if self.watchdog is not None and self.error is None:
+                self.watchdog.stop()
 
     # -- availability ------------------------------------------------------------------------------
     def _pump(self, block: bool) -> bool:
@@ -439,6 +461,8 @@ class StageEngine:
                 return True
             if self.last_batch is not None and b > self.last_batch:
                 return False
+            if self.error is not None:
+                raise EngineError("stopping: a peer rank failed") from self.error
             if not self._pump(block=True):
                 self._check_peers()
                 if time.monotonic() > deadline:

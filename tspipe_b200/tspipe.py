@@ -369,10 +369,16 @@ class TSPipe:
             msg.labels = labels
         max_inflight = int(self.config["runtime"]["max_inflight"])
         while bid - self._done_batches > max_inflight:
-            if self.engine.error is not None:
-                self.engine.join()
+            self._raise_if_failed()
             time.sleep(0.0005)
+        self._raise_if_failed()
         self.engine.inbox.put(msg)
+
+    def _raise_if_failed(self) -> None:
+        err = self.engine.error
+        if err is not None:
+            from .runtime.engine import EngineError
+            raise EngineError(f"pipeline failed on or near rank {self.rank}: {err}") from err
 
     def _stage_inputs(self, views: List[Any]):
         """Start the host-to-device copies of a whole mini-batch on the feeder's own stream; the
@@ -394,11 +400,39 @@ class TSPipe:
         ``max_inflight`` batches ahead of the last reported loss (`tspipe/tspipe.py:486-509`)."""
         if self.mode == "spawn":
             return self.pipeline.poll_loss(self.last_batch_idx, int(self.config["runtime"]["max_inflight"]))
-        if not self.topo.is_last:
-            return None
         lag = self.last_batch_idx - self._losses_returned
         block = lag >= int(self.config["runtime"]["max_inflight"])
-        return self._pop_loss(block)
+        if self.topo.is_last:
+            return self._pop_loss(block)
+        if self.rank == 0:
+            return self._remote_loss(block)
+        return None
+
+    def _loss_publisher(self) -> bool:
+        """The loss stage of replica 0 forwards every loss to rank 0 (the primary) through the store when
+        rank 0 does not hold the loss stage itself."""
+        t = self.topo
+        return t.is_last and t.replica == 0 and t.rank != 0
+
+    def _remote_loss(self, block: bool) -> Optional[float]:
+        import pickle
+        key = f"loss/{self._losses_returned + 1}"
+        store = self.topo.store
+        deadline = time.monotonic() + float(self.config["runtime"]["timeout_s"])
+        while not store.check([key]):
+            if not block:
+                return None
+            self._raise_if_failed()
+            if time.monotonic() > deadline:
+                raise TimeoutError("no loss within runtime.timeout_s")
+            time.sleep(0.001)
+        val = pickle.loads(store.get(key))
+        try:
+            store.delete_key(key)
+        except Exception:
+            pass
+        self._losses_returned += 1
+        return val
 
     def _pop_loss(self, block: bool) -> Optional[float]:
         eng = self.engine
@@ -416,8 +450,13 @@ class TSPipe:
         if isinstance(item, tuple):
             host, ev = item
             ev.synchronize()
-            return float(host)
-        return float(item)
+            val = float(host)
+        else:
+            val = float(item)
+        if self._loss_publisher():
+            import pickle
+            self.topo.store.set(f"loss/{b}", pickle.dumps(val))
+        return val
 
     def flush(self) -> List[float]:
         """Finish every fed batch and leave the pipeline idle but alive (the next ``feed`` refills it).
@@ -430,14 +469,22 @@ class TSPipe:
         self.engine.on_flushed = lambda b: done.set()
         self.engine.inbox.put(FlushMsg(self.last_batch_idx))
         while not done.wait(0.05):
-            if self.engine.error is not None:
-                self.engine.join()
+            self._raise_if_failed()
+        return self._drain_losses()
+
+    def _drain_losses(self) -> List[float]:
+        """Losses not yet handed out.  On rank 0 without the loss stage: wait until the loss stage has
+        published everything up to the last fed batch."""
         rest = []
-        while True:
-            l = self._pop_loss(block=False)
-            if l is None:
-                break
-            rest.append(l)
+        if self.topo.is_last:
+            while True:
+                l = self._pop_loss(block=False)
+                if l is None:
+                    break
+                rest.append(l)
+        elif self.rank == 0 and self.topo.replica == 0:
+            while self._losses_returned < self.last_batch_idx:
+                rest.append(self._remote_loss(block=True))
         return rest
 
     def stop(self) -> List[float]:
@@ -452,14 +499,13 @@ class TSPipe:
         if self.mode == "spawn":
             return self.pipeline.stop(self.last_batch_idx)
         from .runtime.engine import StopMsg
+        self._raise_if_failed()
         self.engine.inbox.put(StopMsg(self.last_batch_idx))
+        while self.engine.thread.is_alive():
+            self.engine.thread.join(0.1)
+            self._raise_if_failed()
         self.engine.join()
-        rest = []
-        while True:
-            l = self._pop_loss(block=False)
-            if l is None:
-                break
-            rest.append(l)
+        rest = self._drain_losses()
         self._collect_final()
         return rest
 
