@@ -111,13 +111,20 @@ struct Cfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTmemCols = BN;                 // power of two >= 32
+  static constexpr int kTmemCols = 2 * BN;             // two accumulator buffers; power of two, <= 512
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // epilogue modes
 constexpr int EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2;
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulator
+// buffers in TMEM let the epilogue of tile i run while the MMAs of tile i+1 are issued; the smem ring keeps
+// streaming across tile boundaries.
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -127,13 +134,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   using C = Cfg<BN>;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(tiles + kStages * C::kStageBytes);
-  uint64_t* full_bar = bars;                 // [kStages]
-  uint64_t* empty_bar = bars + kStages;      // [kStages]
-  uint64_t* tmem_full_bar = bars + 2 * kStages;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 1);
+  uint64_t* full_bar = bars;                         // [kStages]  TMA -> MMA
+  uint64_t* empty_bar = bars + kStages;              // [kStages]  MMA -> TMA
+  uint64_t* tmem_full_bar = bars + 2 * kStages;      // [2]        MMA -> epilogue
+  uint64_t* tmem_empty_bar = bars + 2 * kStages + 2; // [2]        epilogue -> MMA
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tiles_m = (m + BM - 1) / BM, tiles_n = (n + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -141,12 +150,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       mbar_init(full_bar + s, 1);
       mbar_init(empty_bar + s, 1);
     }
-    mbar_init(tmem_full_bar, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar + a, 1);
+      mbar_init(tmem_empty_bar + a, 4);              // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
   }
-  if (warp == 1) {        // one full warp allocates the accumulator columns
+  if (warp == 1) {        // one full warp allocates both accumulator buffers
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((uint32_t)C::kTmemCols)
                  : "memory");
@@ -160,52 +172,72 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t round = kb / kStages;
-        if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1)) break;
-        uint8_t* a_dst = tiles + s * C::kStageBytes;
-        uint8_t* b_dst = a_dst + C::kABytes;
-        mbar_expect_tx(full_bar + s, (uint32_t)C::kStageBytes);
-        tma_load_2d(a_dst, &tmap_a, full_bar + s, kb * BK, m0);
-        tma_load_2d(b_dst, &tmap_b, full_bar + s, kb * BK, n0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1)) { ok = false; break; }
+          uint8_t* a_dst = tiles + s * C::kStageBytes;
+          uint8_t* b_dst = a_dst + C::kABytes;
+          mbar_expect_tx(full_bar + s, (uint32_t)C::kStageBytes);
+          tma_load_2d(a_dst, &tmap_a, full_bar + s, kb * BK, m0);
+          tma_load_2d(b_dst, &tmap_b, full_bar + s, kb * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN);
+      uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t round = kb / kStages;
-        ok = mbar_wait(full_bar + s, round & 1, status, 2);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-        const uint32_t b_addr = a_addr + C::kABytes;
-        const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(b_addr);
-#pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-          umma_bf16(tmem_base, a_desc + (uint64_t)(2 * kk), b_desc + (uint64_t)(2 * kk), idesc,
-                    (kb > 0 || kk > 0) ? 1u : 0u);
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+        const uint32_t acc = lt & 1, use = lt >> 1;
+        if (use > 0) {
+          ok = mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        umma_commit(empty_bar + s);          // smem slot is free once these MMAs have read it
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          ok = mbar_wait(full_bar + s, round & 1, status, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
+          const uint32_t b_addr = a_addr + C::kABytes;
+          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(b_addr);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+            umma_bf16(d_tmem, a_desc + (uint64_t)(2 * kk), b_desc + (uint64_t)(2 * kk), idesc,
+                      (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar + s);          // smem slot is free once these MMAs have read it
+        }
+        umma_commit(tmem_full_bar + acc);      // accumulator complete (or: nothing more will be issued)
       }
-      umma_commit(tmem_full_bar);            // accumulator complete (or: nothing more will be issued)
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lanes 32*(warp%4) .. +31 ----------------
     const int quarter = warp & 3;
-    const bool ok = mbar_wait(tmem_full_bar, 0, status, 3);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = m0 + quarter * 32 + lane;
-    if (ok) {
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      const uint32_t acc = lt & 1, use = lt >> 1;
+      ok = mbar_wait(tmem_full_bar + acc, use & 1, status, 3);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, r);
         const int col = n0 + c0;
         if (row < m && col < n) {
           float v[32];
@@ -233,6 +265,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
+      // this warp has drained its quarter of the accumulator: hand the buffer back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar + acc);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,7 +323,15 @@ int launch(const void* a, const void* b, void* c, const float* bias, int m, int 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm <= 0) n_sm = 148;
+  }
+  const int num_tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
+  const int grid = num_tiles < n_sm ? num_tiles : n_sm;
   kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, (OutT*)c, bias, m, n, k, ldc, epi, status);
   return TSP_LAUNCH_CHECK();
 }
@@ -299,7 +343,8 @@ extern "C" {
 // C[m,n] = A[m,k] * B[n,k]^T (+ bias[n]) (-> GELU).  A, B bf16 row-major with leading dimensions lda / ldb
 // (elements; multiples of 8, base pointers 16-byte aligned); C bf16 (out_dtype 1) or fp32 (0), leading dim ldc.
 // epi: 0 none, 1 bias, 2 bias + GELU.  `status` is one int in device memory, zeroed by the caller; a non-zero
-// value after the kernel means a bounded wait ran out (1 producer, 2 MMA, 3 epilogue) and C is not valid.
+// value after the kernel means a bounded wait ran out (1 producer, 2 MMA on operands, 3 epilogue, 4 MMA on a free
+// accumulator) and C is not valid.
 int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,
                      int ldc, int out_dtype, int epi, int* status, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
