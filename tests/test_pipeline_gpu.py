@@ -127,3 +127,54 @@ def test_moco_replicas_gather_keys_through_peer_memory_and_tcgen05_logits():
     out = run_ranks(_moco_rank, 2, n_steps)
     mean = [(x + y) / 2 for x, y in zip(out[0], out[1])]
     torch.testing.assert_close(torch.tensor(mean), torch.tensor(ref), rtol=2e-2, atol=2e-2)   # bf16 logits
+
+
+def _kd_batches(n):
+    g = torch.Generator().manual_seed(7)
+    return [(torch.randn(64, 3, 32, 32, generator=g), torch.randint(0, 10, (64,), generator=g)) for _ in range(n)]
+
+
+def _split_rank(rank, world, n_steps):
+    import warnings
+    import torch.distributed as dist
+    from tspipe_b200 import TSPipe, TSPipeMode
+    from tspipe_b200.losses import soft_target_kd
+    from tspipe_b200.models.mlp import toy_student, toy_teacher
+    torch.manual_seed(0)
+    teacher, student = toy_teacher(), toy_student()
+    opt = torch.optim.SGD(student.parameters(), lr=0.05)
+    cfg = {"model_split": {"online": [5], "target": [9]},
+           "runtime": {"num_ubatch": 4, "dtype": "fp32", "timeout_s": 120, "placement": "split"},
+           "train": {"deferred_batch_norm": False}}
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        tsp = TSPipe(student, teacher, None, opt, soft_target_kd, None, 1.0, "", config=cfg, device=f"cuda:{rank}",
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False,
+                     extra_args=Namespace(T=4.0, alpha=0.9))
+    losses = []
+    for x, y in _kd_batches(n_steps):
+        l = tsp.feed(x.pin_memory(), x.pin_memory(), y.pin_memory())
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    peer = getattr(tsp.engine, "peer", False)
+    dist.destroy_process_group()
+    return losses, peer
+
+
+def test_split_placement_kd_loss_reads_teacher_logits_from_peer_gpu():
+    """Teacher on cuda:0, student on cuda:1: the fused KD loss kernel on cuda:1 reads the teacher logits from
+    the ring buffer in cuda:0's memory."""
+    from tspipe_b200.losses import soft_target_kd
+    from tspipe_b200.models.mlp import toy_student, toy_teacher
+    from tspipe_b200.oracle import DelayedTeacherOracle
+    n_steps = 5
+    torch.manual_seed(0)
+    teacher, student = toy_teacher(), toy_student()
+    opt = torch.optim.SGD(student.parameters(), lr=0.05)
+    orc = DelayedTeacherOracle(student, teacher, opt, soft_target_kd, None, 1.0, kd=True, n_ubatch=4, bwd_split=1,
+                               extra_args=Namespace(T=4.0, alpha=0.9))
+    ref = [orc.step(x, x, y) for x, y in _kd_batches(n_steps)]
+    out = run_ranks(_split_rank, 2, n_steps)
+    assert out[1][1] is True
+    torch.testing.assert_close(torch.tensor(out[1][0]), torch.tensor(ref), rtol=2e-4, atol=1e-5)

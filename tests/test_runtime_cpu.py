@@ -204,3 +204,41 @@ def test_moco_data_parallel_replicas_gather_keys(pp, dp):
     want = list(full.state_dict().values())
     for a, b in zip(got, want):
         torch.testing.assert_close(a, b.detach(), rtol=2e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------
+def _split_rank(rank, world, n_steps):
+    torch.manual_seed(0)
+    teacher, student = toy_teacher(), toy_student()
+    opt = torch.optim.SGD(student.parameters(), lr=0.05)
+    cfg = {"model_split": {"online": [3, 2], "target": [5, 4]},
+           "runtime": {"num_ubatch": 4, "backend": "gloo", "timeout_s": 60, "placement": "split"},
+           "train": {"deferred_batch_norm": False}}
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        tsp = TSPipe(student, teacher, None, opt, soft_target_kd, None, 1.0, "", config=cfg, device="cpu",
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False, extra_args=KD_ARGS)
+    losses = []
+    for x, y in _toy_batches(n_steps):
+        l = tsp.feed(x, x, y)
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    return losses, tsp.state_dicts()[0]
+
+
+def test_split_placement_teacher_and_student_on_different_ranks():
+    """Toy KD with the 2-stage teacher on ranks 0-1 and the 2-stage student on ranks 2-3: same losses and
+    final student weights as the oracle; rank 0 still receives the losses."""
+    n_steps = 5
+    ref_losses, ref_state = _oracle_kd(n_steps, 4, 1)
+    out = run_ranks(_split_rank, 4, n_steps)
+    torch.testing.assert_close(torch.tensor(out[3][0]), torch.tensor(ref_losses), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(torch.tensor(out[0][0]), torch.tensor(ref_losses), rtol=1e-5, atol=1e-6)
+    merged = {}
+    for st in out[0][1].values():
+        merged.update(st)
+    assert set(merged) == set(ref_state)
+    for k in ref_state:
+        torch.testing.assert_close(merged[k], ref_state[k], rtol=1e-5, atol=1e-6)

@@ -18,6 +18,9 @@ New optional keys (all defaulted so reference YAML files load unchanged):
 ``runtime.max_inflight``     batches the feeder may run ahead (default 3)
 ``runtime.prefetch``         stage-link receives posted ahead of need (default 2)
 ``runtime.peer_memory``      map peer GPUs' buffers for in-kernel NVLink reads (default True on CUDA)
+``runtime.placement``        ``colocated`` (teacher and student stage j share rank j) | ``split`` (teacher stages
+                             on the first ranks of a replica, student stages on the rest; supervised mode)
+``runtime.teacher_slots``    batches the split-placement teacher may run ahead (default 2)
 ``runtime.resume``           checkpoint directory (or ``""``) to resume from
 ``runtime.heartbeat_s`` / ``runtime.timeout_s``  failure-detection heartbeat period / deadline
 """
@@ -36,7 +39,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False},
 }
 
 

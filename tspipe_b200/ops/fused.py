@@ -186,7 +186,10 @@ class _KdCe(torch.autograd.Function):
     @staticmethod
     def forward(ctx, s, t, labels, row_mask, temp, w_ce, w_kd):
         s2 = s.reshape(-1, s.shape[-1]).contiguous()
-        t2 = None if t is None else t.detach().reshape(-1, t.shape[-1]).contiguous()
+        if t is None or not isinstance(t, torch.Tensor):
+            t2 = t          # None, or a peer-mapped [rows, classes] matrix read in place over NVLink
+        else:
+            t2 = t.detach().reshape(-1, t.shape[-1]).contiguous()
         n, c = s2.shape
         loss = torch.zeros((), dtype=torch.float32, device=s.device)
         gs = torch.empty_like(s2)

@@ -212,6 +212,8 @@ class TSPipe:
         init_distributed(rank, world, backend, os.environ.get("MASTER_ADDR", "127.0.0.1"),
                          int(os.environ.get("MASTER_PORT", 29500)), device, self.config["runtime"]["timeout_s"])
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if self.config["runtime"]["placement"] == "split":
+            return self._init_split(device)
         pp, dp = self._resolve_grid(self.world)
         self.topo = build_topology(pp, dp, device, timeout_s=self.config["runtime"]["timeout_s"])
         self._build_partitions(pp)
@@ -235,6 +237,42 @@ class TSPipe:
         self.num_bwd_ubatches = self.engine.U * self.engine.S
         self.mode = "launcher"
         self.engine.start()
+
+    def _init_split(self, device) -> None:
+        """Teacher stages on the first ranks of each replica, student stages on the rest."""
+        from .runtime.split_engine import SplitKDEngine, SplitTopology
+        if self.tspipe_mode != TSPipeMode.SUPERVISED_MOMENTUM or self.target_update_fn is not None:
+            raise ValueError("runtime.placement: split supports supervised mode with a frozen teacher")
+        split = self.config["model_split"]
+        if split["online"] is None or split["target"] is None:
+            raise BalanceError("split placement needs model_split.online and model_split.target")
+        pt_, ps = len(split["target"]), len(split["online"])
+        dp = self.config["runtime"]["dp_replicas"] or self.world // (pt_ + ps)
+        self.topo = SplitTopology(pt_, ps, dp, device, timeout_s=self.config["runtime"]["timeout_s"])
+        if self.config["runtime"]["num_ubatch"] is None:
+            self.config["runtime"]["num_ubatch"] = max(ps - 1, 1)
+        self.config["train"]["deferred_batch_norm"] = False
+        n_on = len(self.module_online) + (len(self.module_predictor) if self.module_predictor is not None else 0)
+        self.partitions_online, self.partitions_target = split_module(
+            self.module_online, self.module_target, self.module_predictor, split["online"], split["target"])
+        self.ema_plans = None
+        t = self.topo
+        part = self.partitions_target[t.stage] if t.is_teacher else self.partitions_online[t.stage]
+        opt = None
+        if not t.is_teacher:
+            rebind_optimizer(self.optimizer, list(part.parameters()))
+            opt = self.optimizer
+        self.engine = SplitKDEngine(t, self.config, part, opt, self.loss_fn, self.target_train_mode,
+                                    self.scatter_gather_fn, self.args, self.extra_args)
+        self.engine.on_batch_done = self._on_batch_done
+        self._done_batches = 0
+        self.num_ubatches = self.num_bwd_ubatches = self.engine.U
+        self.mode = "launcher"
+        self.engine.start()
+
+    def _is_loss_rank(self) -> bool:
+        t = self.topo
+        return bool(getattr(t, "is_loss_rank", t.is_last))
 
     def _build_partitions(self, pp: int) -> None:
         cfg = self.config
@@ -270,7 +308,8 @@ class TSPipe:
         every = int(self.config["train"]["save_model_every_iter"] or 0)
         if every > 0 and b % every == 0 and self.artifact_dir:
             from .ckpt import save_partition
-            save_partition(self.artifact_dir, b, self.topo.stage, self.engine, replica=self.topo.replica)
+            save_partition(self.artifact_dir, b, getattr(self.topo, "local", self.topo.stage), self.engine,
+                           replica=self.topo.replica)
 
     def _maybe_resume(self) -> None:
         path = self.config["runtime"]["resume"]
@@ -365,7 +404,7 @@ class TSPipe:
             msg.views = views
             if topo.is_cuda:
                 msg.views, msg.ready_event = self._stage_inputs(views)
-        if topo.is_last:
+        if self._is_loss_rank():
             msg.labels = labels
         max_inflight = int(self.config["runtime"]["max_inflight"])
         while bid - self._done_batches > max_inflight:
@@ -402,7 +441,7 @@ class TSPipe:
             return self.pipeline.poll_loss(self.last_batch_idx, int(self.config["runtime"]["max_inflight"]))
         lag = self.last_batch_idx - self._losses_returned
         block = lag >= int(self.config["runtime"]["max_inflight"])
-        if self.topo.is_last:
+        if self._is_loss_rank():
             return self._pop_loss(block)
         if self.rank == 0:
             return self._remote_loss(block)
@@ -412,7 +451,7 @@ class TSPipe:
         """The loss stage of replica 0 forwards every loss to rank 0 (the primary) through the store when
         rank 0 does not hold the loss stage itself."""
         t = self.topo
-        return t.is_last and t.replica == 0 and t.rank != 0
+        return self._is_loss_rank() and t.replica == 0 and t.rank != 0
 
     def _remote_loss(self, block: bool) -> Optional[float]:
         import pickle
@@ -476,7 +515,7 @@ class TSPipe:
         """Losses not yet handed out.  On rank 0 without the loss stage: wait until the loss stage has
         published everything up to the last fed batch."""
         rest = []
-        if self.topo.is_last:
+        if self._is_loss_rank():
             while True:
                 l = self._pop_loss(block=False)
                 if l is None:
@@ -522,8 +561,10 @@ class TSPipe:
         self.final_target_state: Dict[int, Dict[str, torch.Tensor]] = {}
         for item in gathered:
             if item is not None:
-                self.final_online_state[item[0]] = item[1]
-                self.final_target_state[item[0]] = item[2]
+                if item[1]:
+                    self.final_online_state[item[0]] = item[1]
+                if item[2]:
+                    self.final_target_state[item[0]] = item[2]
 
     def state_dicts(self) -> Tuple[Dict[int, Dict[str, torch.Tensor]], Dict[int, Dict[str, torch.Tensor]]]:
         """``(online, target)``: per-partition state dicts after :meth:`stop`."""
