@@ -242,3 +242,35 @@ def test_split_placement_teacher_and_student_on_different_ranks():
     assert set(merged) == set(ref_state)
     for k in ref_state:
         torch.testing.assert_close(merged[k], ref_state[k], rtol=1e-5, atol=1e-6)
+
+
+def _async_rank(rank, world, enabled):
+    import warnings
+    torch.manual_seed(0)
+    student = mlp_sequential([12, 16, 4])
+    teacher = mlp_sequential([12, 8, 4])
+    opt = torch.optim.SGD(student.parameters(), lr=0.5)
+    cfg = {"model_split": {"online": [3], "target": [3]}, "async_param_update_emulation": {"enabled": enabled},
+           "runtime": {"num_ubatch": 2, "bwd_split": 1, "backend": "gloo", "timeout_s": 60},
+           "train": {"deferred_batch_norm": False}}
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        tsp = TSPipe(student, teacher, None, opt, soft_target_kd, None, 1.0, "", config=cfg, device="cpu",
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False, extra_args=KD_ARGS)
+    g = torch.Generator().manual_seed(9)
+    x, y = torch.randn(8, 12, generator=g), torch.randint(0, 4, (8,), generator=g)
+    losses = [tsp.feed(x, x, y) for _ in range(5)]
+    losses = [l for l in losses if l is not None] + tsp.stop()
+    return losses
+
+
+def test_async_param_update_emulation_makes_the_student_one_step_stale():
+    """With the emulation on, batch b runs on the parameters of version b-2: feeding the same batch
+    repeatedly, batches 1 and 2 (both on version 0) give the same loss, batch 3 (version 1) a lower one;
+    without it every step improves."""
+    on = run_ranks(_async_rank, 1, True)[0]
+    off = run_ranks(_async_rank, 1, False)[0]
+    assert len(on) == 5 and len(off) == 5
+    assert abs(on[0] - on[1]) < 1e-7 and on[2] < on[1]
+    assert off[1] < off[0] - 1e-4
+    assert abs(on[2] - off[1]) < 1e-6          # version 1 is the same in both runs

@@ -293,6 +293,9 @@ class StageEngine:
         self._flushing = False
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
+        self.async_emu = bool(config["async_param_update_emulation"]["enabled"]) and not gp["enabled"]
+        self._alt_params = None
+        self._initial_params = self.flat_online.data.clone() if self.async_emu else None
         self.watchdog = None
         self._amp_open = False
         self.error: Optional[BaseException] = None
@@ -821,6 +824,16 @@ class StageEngine:
             if self.optimizer is not None:
                 self.optimizer.step()
             self.updater.step(self.momentum)
+            if self.async_emu:
+                # `async_param_update_emulation` (`tspipe/gpu_task.py:58-66,351-356`): the student of batch b
+                # runs on version b-2 as well, i.e. two interleaved parameter trajectories.  The live buffer now
+                # holds version b; park it and bring back version b-1 for the next batch.
+                if self._alt_params is None:
+                    self._alt_params = self._initial_params
+                    self._initial_params = None
+                tmp = self.flat_online.data.clone()
+                self.flat_online.data.copy_(self._alt_params)
+                self._alt_params = tmp
             self.flat_online.zero_grad()
             if self._amp_open:
                 torch.clear_autocast_cache()
