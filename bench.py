@@ -52,6 +52,8 @@ def parse():
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--image", type=int, default=224)
+    p.add_argument("--trace", action="store_true", help="print per-operation device time totals of the timed pass")
+    p.add_argument("--no-peer", action="store_true", help="NCCL all-reduce instead of the peer-memory DP kernels")
     return p.parse_args()
 
 
@@ -155,9 +157,15 @@ def run_ours(a):
     on_split, tg_split = SPLITS[pp]
     cfg = {"model_split": {"online": on_split, "target": tg_split},
            "runtime": {"num_ubatch": ub, "bwd_split": split, "dp_replicas": dp, "dtype": "bf16",
-                       "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300},
+                       "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300,
+                       "peer_memory": not a.no_peer},
            "train": {"deferred_batch_norm": True}}
-    tsp = TSPipe(online, target, predictor, opt, byol_loss, ema_update, 0.996, "", config=cfg, device=dev)
+    prof = None
+    if a.trace:
+        from tspipe_b200.profiler import TSPipeProfiler
+        prof = TSPipeProfiler(filename=f"/tmp/bench_trace_{rank}.csv").__enter__()
+    tsp = TSPipe(online, target, predictor, opt, byol_loss, ema_update, 0.996, "", config=cfg, device=dev,
+                 profiler=prof)
     topo = tsp.topo
     replica_batch = global_batch // dp
     shape = (replica_batch, 3, a.image, a.image)
@@ -209,7 +217,16 @@ def run_ours(a):
     for i in range(a.warmup):
         feed(i, False)
     tsp.flush()
+    if prof is not None:
+        prof.device_events.clear()
     ms, wall_ms, losses, clocks, launches = timed(a.steps, False, ClockSampler(local) if rank == 0 else None)
+    if prof is not None:
+        tot = {}
+        for op, row, dms in prof.device_times():
+            tot[op] = tot.get(op, 0.0) + dms
+        print(f"[trace rank {rank} stage {topo.stage} replica {topo.replica}] per-step device ms: " +
+              ", ".join(f"{k}={v / a.steps:.2f}" for k, v in sorted(tot.items())), flush=True)
+        prof.device_events.clear()
     value = global_batch * a.steps / (ms / 1e3)
     out = {"metric": "BYOL ResNet-50 training throughput", "value": round(value, 2), "unit": "images/s",
            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms / a.steps, 3),

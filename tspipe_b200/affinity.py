@@ -47,13 +47,16 @@ class AffinityManager:
         allowed = list(allowed if allowed is not None else cls.allowed_cores())
         per = max(1, min(cls.CORES_PER_WORKER, len(allowed) // max(n_workers + 1, 1)))
         free = list(allowed)
-        out: List[List[int]] = []
-        for w in range(n_workers):
-            pref = [c for c in free if local and local[w] and c in local[w]]
-            pick = (pref + [c for c in free if c not in pref])[:per]
-            for c in pick:
-                free.remove(c)
-            out.append(sorted(pick))
+        out: List[List[int]] = [[] for _ in range(n_workers)]
+        for w in range(n_workers):                 # first the cores that are local to each worker's GPU
+            if local and local[w]:
+                for c in [c for c in free if c in local[w]][:per]:
+                    free.remove(c)
+                    out[w].append(c)
+        for w in range(n_workers):                 # then fill up from whatever is left
+            while len(out[w]) < per and free:
+                out[w].append(free.pop(0))
+            out[w].sort()
         return out
 
     @classmethod

@@ -57,8 +57,7 @@ def verify_module(module: nn.Sequential) -> None:
     """`tspipe/utils.py:48-67`: a cut-able model is an ``nn.Sequential`` without duplicate children."""
     if not isinstance(module, nn.Sequential):
         raise TypeError("module must be nn.Sequential to be partitioned")
-    named = list(module.named_children())
-    if len(named) != len({id(m) for _, m in named}):
+    if len(list(module.named_children())) != len(module):       # named_children() drops repeated modules
         raise ValueError("module with duplicate children is not supported")
 
 
