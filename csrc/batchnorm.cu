@@ -38,7 +38,7 @@ __host__ __device__ inline Tile make_tile(int cpv) {
 // grid = (row blocks, channel slabs); block = tx_n * ty_n threads; smem = ty_n * tx_n * 16 floats.
 // ---------------------------------------------------------------------------------------------
 template <typename T, int MODE>
-__global__ void __launch_bounds__(kBlock) bn_colsum_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+__global__ void __launch_bounds__(kBlock, MODE == 0 ? 5 : 2) bn_colsum_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                                            const T* __restrict__ y, T* __restrict__ dres,
                                                            const float* __restrict__ mean_rstd,
                                                            const float* __restrict__ w, const float* __restrict__ bias,
@@ -74,15 +74,17 @@ __global__ void __launch_bounds__(kBlock) bn_colsum_kernel(const T* __restrict__
     const int64_t col = (int64_t)cg * 8;
     int64_t r = r_begin + ty;
     if (MODE == 0) {
-      // eight independent 16/32-byte loads in flight per thread before any arithmetic
+      // eight independent 16/32-byte loads in flight per thread before any arithmetic (raw registers)
       for (; r + 7 * step < r_end; r += 8 * step) {
-        float v[8][8];
+        tsp::Raw8<T> raw[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) tsp::ld8(x, (r + u * step) * c + col, v[u]);
+        for (int u = 0; u < 8; ++u) tsp::ldraw(x, (r + u * step) * c + col, raw[u]);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
+          float v[8];
+          tsp::cvt8(raw[u], v);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) { a[e] += v[u][e]; b[e] += v[u][e] * v[u][e]; }
+          for (int e = 0; e < 8; ++e) { a[e] += v[e]; b[e] += v[e] * v[e]; }
         }
       }
       for (; r < r_end; r += step) {

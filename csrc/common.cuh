@@ -89,6 +89,26 @@ template <> __device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p,
   *reinterpret_cast<uint4*>(p + i) = raw;
 }
 
+// Raw 8-element vectors: issue the loads first (few registers), convert when consumed.
+template <typename T> struct Raw8;
+template <> struct Raw8<float> { float4 a, b; };
+template <> struct Raw8<__nv_bfloat16> { uint4 a; };
+__device__ __forceinline__ void ldraw(const float* p, int64_t i, Raw8<float>& r) {
+  r.a = *reinterpret_cast<const float4*>(p + i);
+  r.b = *reinterpret_cast<const float4*>(p + i + 4);
+}
+__device__ __forceinline__ void ldraw(const __nv_bfloat16* p, int64_t i, Raw8<__nv_bfloat16>& r) {
+  r.a = *reinterpret_cast<const uint4*>(p + i);
+}
+__device__ __forceinline__ void cvt8(const Raw8<float>& r, float (&v)[8]) {
+  v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+}
+__device__ __forceinline__ void cvt8(const Raw8<__nv_bfloat16>& r, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r.a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+}
+
 }  // namespace tsp
 
 // Every launcher returns the cudaError_t of its launch as int (0 = ok).
