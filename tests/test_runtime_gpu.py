@@ -63,3 +63,49 @@ def test_single_gpu_byol_matches_oracle():
     got_t = [v for k, v in tg_state[0].items() if "running" not in k and "num_batches" not in k]
     for a, b in zip(got_t, want_t):
         torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-5)
+
+
+def _spawn_loss(o1, o2, t1, t2, args, extra):
+    from tspipe_b200.losses import byol_loss
+    return byol_loss(o1, o2, t1, t2)
+
+
+def test_spawn_mode_worker_per_gpu(tmp_path):
+    """The reference's launch style: one user process constructs TSPipe with the four CLI flags and the
+    runtime spawns one worker process per visible GPU (here: all of them as pipeline stages)."""
+    import torch.distributed as dist
+    from tspipe_b200 import TSPipe
+    from tspipe_b200.losses import ema_update
+    from tspipe_b200.models.mlp import mlp_sequential
+    from tspipe_b200.optim import LARS
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    n = torch.cuda.device_count()
+    torch.manual_seed(0)
+    online = mlp_sequential([48, 64, 64, 32] + [32] * max(n - 1, 0), batch_norm=True)
+    target = copy.deepcopy(online)
+    pred = nn.Sequential(nn.Linear(32, 32), nn.ReLU(), nn.Linear(32, 32))
+    opt = LARS(list(online.parameters()) + list(pred.parameters()), lr=0.2, weight_decay=1e-4)
+    from tspipe_b200.tspipe import default_balance
+    cfg = tmp_path / "t.yaml"
+    cfg.write_text(f"""
+tspipe:
+  train: {{deferred_batch_norm: True, save_model_every_iter: 2}}
+  model_split: {{online: {default_balance(len(online) + 3, n)}, target: {default_balance(len(target), n)}}}
+  runtime: {{num_ubatch: 2, bwd_split: 1, dtype: fp32, timeout_s: 120}}
+""")
+    tsp = TSPipe(online, target, pred, opt, _spawn_loss, ema_update, 0.9, str(tmp_path),
+                 argv=[f"--tspipe-config={cfg}", "--ip=127.0.0.1", "--rank=0", "--num-nodes=1"])
+    g = torch.Generator().manual_seed(1)
+    losses = []
+    for _ in range(4):
+        l = tsp.feed(torch.randn(16, 48, generator=g).share_memory_(), torch.randn(16, 48, generator=g).share_memory_())
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    assert len(losses) == 4 and all(l == l for l in losses)
+    on, tg = tsp.state_dicts()
+    assert len(on) == n and len(tg) == n
+    assert (tmp_path / "model_batch2_part0.pt").exists()

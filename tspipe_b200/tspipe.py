@@ -211,6 +211,11 @@ class TSPipe:
         init_distributed(rank, world, backend, os.environ.get("MASTER_ADDR", "127.0.0.1"),
                          int(os.environ.get("MASTER_PORT", 29500)), device, self.config["runtime"]["timeout_s"])
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", self.world))
+        if local_world < self.world and self.config["runtime"]["peer_memory"]:
+            # ranks span several nodes: peer-mapped buffers only exist inside a node, use the collectives
+            Log.i("multi-node job: peer-memory paths disabled, NCCL collectives are used instead")
+            self.config["runtime"]["peer_memory"] = False
         if self.config["runtime"]["placement"] == "split":
             return self._init_split(device)
         pp, dp = self._resolve_grid(self.world)
