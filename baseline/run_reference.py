@@ -31,7 +31,7 @@ REF = os.path.join(HERE, "_ref")
 
 SPLITS = {   # 30 online children (26 + 4 predictor) / 26 target children
     1: ([30], [26]),
-    2: ([11, 19], [11, 15]),
+    2: ([8, 22], [8, 18]),
     4: ([6, 5, 7, 12], [6, 5, 7, 8]),
     8: ([5, 2, 3, 3, 3, 3, 4, 7], [5, 2, 3, 3, 3, 3, 4, 3]),
 }

@@ -51,7 +51,9 @@ def parse():
     p.add_argument("--model", default="resnet50")
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-pipeline", action="store_true", help="skip the secondary two-stage pipeline measurement")
     p.add_argument("--image", type=int, default=224)
+    p.add_argument("--split", default="", help="override model_split, e.g. 9,21/9,17 (online/target)")
     p.add_argument("--trace", action="store_true", help="print per-operation device time totals of the timed pass")
     p.add_argument("--no-peer", action="store_true", help="NCCL all-reduce instead of the peer-memory DP kernels")
     return p.parse_args()
@@ -103,24 +105,25 @@ class ClockSampler:
 
 
 def default_grid(n: int):
-    """(pp, dp, ubatch, bwd_split) per GPU count: the interleaved pipeline is two stages deep and the
-    remaining GPUs replicate it (ResNet-50 is far below one B200's memory; deeper pipelines only add
-    fill/drain and imbalance, so the spare GPUs go to data parallelism)."""
-    if n == 1:
-        return 1, 1, 1, 1
-    return 2, n // 2, 2, 1
+    """(pp, dp, ubatch, bwd_split) per GPU count.  ResNet-50 (33 M parameters) is far below one B200's
+    memory, so the headline number replicates the single-stage teacher/student step on every GPU (gradient
+    reduce-scatter + LARS + all-gather through peer memory); the interleaved two-stage pipeline on the same
+    job is measured next to it (``pipeline`` in the output, ``--pp 2`` to make it the main number)."""
+    return 1, n, 1, 1
 
 
 # ResNet-50 online net = 26 trunk+projector children + 4 predictor children; target = 26.
 SPLITS = {
     1: ([30], [26]),
-    2: ([11, 19], [11, 15]),
+    2: ([8, 22], [8, 18]),
     4: ([6, 5, 7, 12], [6, 5, 7, 8]),
     8: ([5, 2, 3, 3, 3, 3, 4, 7], [5, 2, 3, 3, 3, 3, 4, 3]),
 }
 
 
-def run_ours(a):
+def measure(a, pp, dp, ub, split, e2e):
+    """Build the BYOL ResNet-50 job on a ``dp x pp`` grid, warm up, time K steps; returns a result dict."""
+    import gc
     import torch
     import torch.distributed as dist
     from tspipe_b200 import TSPipe
@@ -132,22 +135,7 @@ def run_ours(a):
     world = int(os.environ.get("WORLD_SIZE", 1))
     rank = int(os.environ.get("RANK", 0))
     local = int(os.environ.get("LOCAL_RANK", 0))
-    assert world == a.gpus, f"launched with {world} ranks for --gpus {a.gpus}"
-    os.environ.setdefault("RANK", "0")
-    os.environ.setdefault("WORLD_SIZE", "1")
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29577")
-    torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    torch.backends.cudnn.benchmark = True
-    torch.backends.cuda.matmul.allow_tf32 = True
-    torch.backends.cudnn.allow_tf32 = True
-
-    pp, dp, ub, split = default_grid(world)
-    if a.pp:
-        pp, dp = a.pp, world // a.pp
-    ub = a.ubatch or ub
-    split = a.bwd_split or split
     torch.manual_seed(0)
     online, target, predictor = byol_networks(a.model, 4096, 256)
     params = list(online.parameters()) + list(predictor.parameters())
@@ -155,6 +143,8 @@ def run_ours(a):
     lr = 0.2 * global_batch / 256
     opt = LARS(params, lr=lr, weight_decay=1.5e-6, momentum=0.9)
     on_split, tg_split = SPLITS[pp]
+    if a.split and pp > 1:
+        on_split, tg_split = ([int(x) for x in part.split(",")] for part in a.split.split("/"))
     cfg = {"model_split": {"online": on_split, "target": tg_split},
            "runtime": {"num_ubatch": ub, "bwd_split": split, "dp_replicas": dp, "dtype": "bf16",
                        "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300,
@@ -169,11 +159,9 @@ def run_ours(a):
     topo = tsp.topo
     replica_batch = global_batch // dp
     shape = (replica_batch, 3, a.image, a.image)
-
     g = torch.Generator().manual_seed(1234 + topo.replica)
     n_host = 2
-    host_views = None
-    dev_views = None
+    host_views = dev_views = None
     if topo.is_first:
         host_views = [(torch.randn(shape, generator=g).pin_memory(), torch.randn(shape, generator=g).pin_memory())
                       for _ in range(n_host)]
@@ -213,8 +201,7 @@ def run_ours(a):
         dist.all_reduce(n_launch)
         return t[0].item(), t[1].item(), losses, clocks, int(n_launch.item())
 
-    # warm-up (untimed): W steps through the device-resident path and W through the host path
-    for i in range(a.warmup):
+    for i in range(a.warmup):          # untimed warm-up
         feed(i, False)
     tsp.flush()
     if prof is not None:
@@ -227,19 +214,11 @@ def run_ours(a):
         print(f"[trace rank {rank} stage {topo.stage} replica {topo.replica}] per-step device ms: " +
               ", ".join(f"{k}={v / a.steps:.2f}" for k, v in sorted(tot.items())), flush=True)
         prof.device_events.clear()
-    value = global_batch * a.steps / (ms / 1e3)
-    out = {"metric": "BYOL ResNet-50 training throughput", "value": round(value, 2), "unit": "images/s",
-           "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms / a.steps, 3),
-           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-           "impl": "ours", "gpu_launches": launches, "clocks": clocks,
-           "config": {"model": f"byol_{a.model}+mlp4096-256", "global_batch": global_batch, "seq_len": None,
-                      "image": a.image, "parallelism": f"dp{dp}xpp{pp}", "microbatches": ub, "bwd_split": split,
-                      "optimizer": "LARS", "ema": 0.996, "l2_policy": "inputs larger than L2 (154 MB per replica step)",
-                      "timing": "CUDA events on the compute stream around K feeds + flush, max over ranks"}}
-    if topo.is_last and losses:
-        out["last_loss"] = round(losses[-1], 5)
-    if not a.no_e2e:
-        for i in range(min(a.warmup, 2)):
+    out = {"value": round(global_batch * a.steps / (ms / 1e3), 2), "ms_per_step": round(ms / a.steps, 3),
+           "gpu_launches": launches, "clocks": clocks, "parallelism": f"dp{dp}xpp{pp}", "microbatches": ub,
+           "bwd_split": split, "global_batch": global_batch, "last_loss": round(losses[-1], 5) if losses else None}
+    if e2e:
+        for i in range(min(a.warmup, 3)):
             feed(i, True)
         tsp.flush()
         ms2, wall2, losses2, _, _ = timed(a.steps, True)
@@ -248,6 +227,55 @@ def run_ours(a):
                       "ms_per_step": round(max(ms2, wall2) / a.steps, 3),
                       "api": "TSPipe.feed(pinned host views) per step; loss read back per step; TSPipe.flush at the end"}
     tsp.stop()
+    if prof is not None:
+        prof.__exit__(None, None, None)
+    del tsp, online, target, predictor, opt, host_views, dev_views
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    assert world == a.gpus, f"launched with {world} ranks for --gpus {a.gpus}"
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    os.environ.setdefault("TORCH_NCCL_SHOW_EAGER_INIT_P2P_SERIALIZATION_WARNING", "false")
+    torch.cuda.set_device(local)
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.allow_tf32 = True
+
+    pp, dp, ub, split = default_grid(world)
+    if a.pp:
+        pp, dp = a.pp, world // a.pp
+        ub = 1 if pp == 1 else 2
+    ub = a.ubatch or ub
+    split = a.bwd_split or split
+    r = measure(a, pp, dp, ub, split, e2e=not a.no_e2e)
+    out = {"metric": "BYOL ResNet-50 training throughput", "value": r["value"], "unit": "images/s",
+           "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": r["ms_per_step"],
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "impl": "ours", "gpu_launches": r["gpu_launches"], "clocks": r["clocks"],
+           "config": {"model": f"byol_{a.model}+mlp4096-256", "global_batch": r["global_batch"], "seq_len": None,
+                      "image": a.image, "parallelism": r["parallelism"], "microbatches": r["microbatches"],
+                      "bwd_split": r["bwd_split"], "optimizer": "LARS", "ema": 0.996,
+                      "l2_policy": "inputs larger than L2 (154 MB per replica step)",
+                      "timing": "CUDA events on the compute stream around K feeds + flush, max over ranks"}}
+    if r.get("last_loss") is not None:
+        out["last_loss"] = r["last_loss"]
+    if "e2e" in r:
+        out["e2e"] = r["e2e"]
+    if world >= 2 and pp == 1 and not a.no_pipeline:
+        # the same job on the interleaved two-stage teacher/student pipeline (x world/2 replicas)
+        p2 = measure(a, 2, world // 2, 2, split, e2e=False)
+        out["pipeline"] = {k: p2[k] for k in ("value", "ms_per_step", "parallelism", "microbatches", "gpu_launches")}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if dist.is_initialized():

@@ -90,6 +90,9 @@ def init_distributed(rank: int, world: int, backend: str, master_addr: str, mast
                             timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
 
 
+_instances = 0
+
+
 def build_topology(pp: int, dp: int, device: torch.device, backend: Optional[str] = None,
                    timeout_s: float = 600.0) -> Topology:
     """Create every subgroup.  All ranks call this collectively, in the same order."""
@@ -119,5 +122,7 @@ def build_topology(pp: int, dp: int, device: torch.device, backend: Optional[str
             if rank in ranks:
                 topo.dp_group = g
     from torch.distributed.distributed_c10d import _get_default_store
-    topo.store = dist.PrefixStore("tspipe_ctl", _get_default_store())
+    global _instances
+    _instances += 1             # every TSPipe instance of a job gets its own key space in the store
+    topo.store = dist.PrefixStore(f"tspipe_ctl{_instances}", _get_default_store())
     return topo
