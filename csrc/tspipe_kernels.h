@@ -69,6 +69,12 @@ int tsp_dp_lars_apply(void* const* params, int n_peers, int self, const float* g
 int tsp_dp_adamw_step(void* const* grads, void* const* params, int n_peers, int self, float scale, float* m, float* v,
                       const int64_t* chunks, int n_chunks, const float* seg_hp, cudaStream_t stream);
 
+// ---- pool.cu ------------------------------------------------------------------------------------------------------
+int tsp_maxpool3x3s2_fwd(const void* x, void* y, uint8_t* idx, int n, int h, int w, int c, int dtype,
+                         cudaStream_t stream);
+int tsp_maxpool3x3s2_bwd(const void* dy, const uint8_t* idx, void* dx, int n, int h, int w, int c, int dtype,
+                         cudaStream_t stream);
+
 // ---- gemm_tcgen05.cu ------------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,
                      int ldc, int out_dtype, int epi, int* status, cudaStream_t stream);

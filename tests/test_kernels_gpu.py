@@ -337,3 +337,20 @@ def test_dp_fused_step_two_replicas_one_process(opt_name):
             for i, q in enumerate(ref_ps):
                 got = f.data[f.offsets[i]: f.offsets[i] + f.numels[i]].view(q.shape).cpu()
                 torch.testing.assert_close(got, q.detach(), rtol=3e-5, atol=3e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 64, 112, 112), (2, 16, 7, 9), (3, 8, 2, 2)])
+def test_maxpool_channels_last(dtype, shape):
+    from tspipe_b200.ops.pool import MaxPool3x3s2
+    torch.manual_seed(12)
+    x = torch.randn(shape, device=_dev()).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_()
+    pool = MaxPool3x3s2()
+    y = pool(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = F.max_pool2d(xr, 3, 2, 1)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr.detach(), rtol=0, atol=0)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=1e-2, atol=1e-2)

@@ -15,6 +15,7 @@ import torch
 from torch import nn
 
 from ..ops.bn import bn_act
+from ..ops.pool import MaxPool3x3s2
 
 
 class Bottleneck(nn.Module):
@@ -72,7 +73,7 @@ def resnet_trunk_children(name: str = "resnet50") -> "OrderedDict[str, nn.Module
     ch["conv1"] = nn.Conv2d(3, 64, 7, stride=2, padding=3, bias=False)
     ch["bn1"] = nn.BatchNorm2d(64)
     ch["relu"] = nn.ReLU()
-    ch["maxpool"] = nn.MaxPool2d(3, stride=2, padding=1)
+    ch["maxpool"] = MaxPool3x3s2()
     inplanes = 64
     for li, (planes, n) in enumerate(zip([64, 128, 256, 512], layers)):
         for bi in range(n):
