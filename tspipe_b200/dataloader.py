@@ -23,13 +23,17 @@ class FastDataLoader(DataLoader):
         super().__init__(*args, **kwargs)
 
 
-def _producer(loader_args, loader_kwargs, q, epochs):
+_EPOCH_END, _ALL_DONE = "__epoch_end__", "__all_done__"
+
+
+def _producer(loader_args, loader_kwargs, q, epochs, done):
     loader = DataLoader(*loader_args, **loader_kwargs)
     for _ in range(epochs):
         for batch in loader:
             q.put(batch)
-        q.put(StopIteration)
-    q.put(None)
+        q.put(_EPOCH_END)
+    q.put(_ALL_DONE)
+    done.wait(600)          # shared-memory tensors in flight die with this process: leave only when told
 
 
 class SuperFastDataLoader:
@@ -47,7 +51,9 @@ class SuperFastDataLoader:
     def _start(self) -> None:
         ctx = torch.multiprocessing.get_context("spawn")
         self._q = ctx.Queue(self.prefetch)
-        self._proc = ctx.Process(target=_producer, args=(self.args, self.kwargs, self._q, self.epochs), daemon=True)
+        self._done = ctx.Event()
+        self._proc = ctx.Process(target=_producer, args=(self.args, self.kwargs, self._q, self.epochs, self._done),
+                                 daemon=True)
         self._proc.start()
 
     def __iter__(self) -> Iterator[Any]:
@@ -55,7 +61,10 @@ class SuperFastDataLoader:
             self._start()
         while True:
             item = self._q.get()
-            if item is StopIteration or item is None:
+            if isinstance(item, str) and item == _ALL_DONE:
+                self._done.set()
+                return
+            if isinstance(item, str) and item == _EPOCH_END:
                 return
             yield item
 
