@@ -51,6 +51,7 @@ def parse():
     p.add_argument("--model", default="resnet50")
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--cuda-graphs", action="store_true", help="replay teacher stage forwards from CUDA graphs")
     p.add_argument("--no-pipeline", action="store_true", help="skip the secondary two-stage pipeline measurement")
     p.add_argument("--image", type=int, default=224)
     p.add_argument("--split", default="", help="override model_split, e.g. 9,21/9,17 (online/target)")
@@ -148,7 +149,7 @@ def measure(a, pp, dp, ub, split, e2e):
     cfg = {"model_split": {"online": on_split, "target": tg_split},
            "runtime": {"num_ubatch": ub, "bwd_split": split, "dp_replicas": dp, "dtype": "bf16",
                        "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300,
-                       "peer_memory": not a.no_peer},
+                       "peer_memory": not a.no_peer, "cuda_graphs": a.cuda_graphs},
            "train": {"deferred_batch_norm": True}}
     prof = None
     if a.trace:

@@ -24,7 +24,7 @@ from torch import nn
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 from tspipe_b200 import TSPipe, TSPipeMode  # noqa: E402
-from tspipe_b200.losses import soft_target_kd  # noqa: E402
+from tspipe_b200.losses import logits_kd, soft_target_kd  # noqa: E402
 from tspipe_b200.models.resnet import resnet_trunk_children, trunk_width  # noqa: E402
 from tspipe_b200.models.vit import vit_classifier  # noqa: E402
 from tspipe_b200.optim import SGD, AdamW  # noqa: E402
@@ -33,6 +33,9 @@ from tspipe_b200.optim import SGD, AdamW  # noqa: E402
 def create_model(name: str, num_classes: int) -> nn.Sequential:
     if name.startswith("vit"):
         return vit_classifier(name, num_classes)
+    if name.startswith("efficientnet"):
+        from tspipe_b200.models.efficientnet import EfficientNet
+        return EfficientNet(name, num_classes).to_sequential()
     if name.startswith("resnet"):
         ch = resnet_trunk_children(name)
         ch["fc"] = nn.Linear(trunk_width(name), num_classes)
@@ -54,6 +57,7 @@ def main() -> None:
     ap.add_argument("--iters-per-epoch", type=int, default=30)
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "sgd"])
+    ap.add_argument("--kd-mode", default="st", choices=["st", "logits"])
     ap.add_argument("--T", type=float, default=4.0)
     ap.add_argument("--lambda-kd", type=float, default=0.9)
     ap.add_argument("--image", type=int, default=224)
@@ -64,7 +68,8 @@ def main() -> None:
     tnet, snet = create_model(args.t_name, args.num_class), create_model(args.s_name, args.num_class)
     opt = AdamW(snet.parameters(), lr=args.lr, weight_decay=0.05) if args.optimizer == "adamw" else \
         SGD(snet.parameters(), lr=args.lr, momentum=0.9, weight_decay=1e-4, nesterov=True)
-    tsp = TSPipe(snet, tnet, None, opt, soft_target_kd, None, 1.0, args.artifact_dir,
+    tsp = TSPipe(snet, tnet, None, opt, soft_target_kd if args.kd_mode == "st" else logits_kd, None, 1.0,
+                 args.artifact_dir,
                  tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False,
                  extra_args=Namespace(T=args.T, alpha=args.lambda_kd))
     g = torch.Generator().manual_seed(0)

@@ -170,3 +170,22 @@ def test_ema_plan_for_different_cuts():
     bad = nn.Sequential(nn.Linear(4, 5))
     with pytest.raises(ValueError):
         build_ema_plans([bad], [nn.Sequential(target[0])])
+
+
+def test_efficientnet_sequential_equals_module_and_logits_loss():
+    from argparse import Namespace
+    from tspipe_b200.losses import logits_kd
+    from tspipe_b200.models.efficientnet import EfficientNet, drop_connect
+    torch.manual_seed(0)
+    net = EfficientNet("efficientnet-tiny-test", num_classes=7)
+    assert net.test_sequential_validity((2, 3, 32, 32), rtol=1e-4, atol=1e-5)
+    seq = net.to_sequential()
+    assert len(seq) == 3 + len(net.blocks) + 3 + 4
+    x = torch.ones(8, 2, 1, 1)
+    assert drop_connect(x, 0.5, False) is x
+    y = drop_connect(x, 0.5, True)
+    assert set(y.flatten().tolist()) <= {0.0, 2.0}
+    s, t = torch.randn(4, 7, requires_grad=True), torch.randn(4, 7)
+    l = logits_kd(s, t, torch.tensor([0, 1, 2, 3]), extra_args=Namespace(lambda_kd=0.5))
+    l.backward()
+    assert s.grad is not None and l.item() > 0

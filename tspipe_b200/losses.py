@@ -37,6 +37,16 @@ def soft_target_kd(student_out, teacher_out, labels, args=None, extra_args=None,
     return (1.0 - alpha) * ce + alpha * kd
 
 
+def logits_kd(student_out, teacher_out, labels, args=None, extra_args=None, epoch: int = 0):
+    """"Do deep nets really need to be deep": MSE between student and teacher logits plus CE
+    (`benchmarks/soft_target/kd_losses/logits.py:17-20`, `train_kd.py:448-453`)."""
+    lam = float(getattr(extra_args, "lambda_kd", getattr(extra_args, "alpha", 0.9)))
+    t = teacher_out if isinstance(teacher_out, torch.Tensor) else None
+    if t is None:
+        raise TypeError("logits_kd needs the teacher logits as a tensor")
+    return (1.0 - lam) * F.cross_entropy(student_out.float(), labels) + lam * F.mse_loss(student_out.float(), t.float())
+
+
 def regression_loss(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     x = F.normalize(x.float(), dim=1)
     y = F.normalize(y.float(), dim=1)

@@ -293,6 +293,7 @@ class StageEngine:
         self._flushing = False
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
+        self._teacher_graphs: Dict[Any, Any] = {}
         self.async_emu = bool(config["async_param_update_emulation"]["enabled"]) and not gp["enabled"]
         self._alt_params = None
         self._initial_params = self.flat_online.data.clone() if self.async_emu else None
@@ -653,8 +654,7 @@ class StageEngine:
                 if self.channels_last:
                     x = pt.tree_map_tensors(_to_channels_last, x)
                 if teacher:
-                    with torch.no_grad(), self._amp():
-                        y = module(x)
+                    y = self._teacher_forward(module, x)
                     self.bn_group_target.step()
                 else:
                     with self._amp():
@@ -677,6 +677,42 @@ class StageEngine:
                     self.t_out.setdefault(key, [None] * self.U)[op.ub] = outs[0]
                 else:
                     self.o_out.setdefault(key, [None] * self.U)[op.ub] = outs
+
+    def _teacher_forward(self, module: nn.Module, x: Any) -> Any:
+        """Teacher stage forward (no autograd).  With ``runtime.cuda_graphs`` the whole stage forward of a
+        given input shape is captured once into a CUDA graph and replayed afterwards: one launch per
+        microbatch instead of several hundred (weights are re-cast inside the graph, BatchNorm statistics
+        accumulate on the device; only the commit counter lives on the host)."""
+        use_graph = (self.cuda and self.cfg["runtime"].get("cuda_graphs", False) and isinstance(x, torch.Tensor)
+                     and not any(isinstance(m, nn.Dropout) and m.p > 0 and m.training for m in module.modules()))
+        if not use_graph:
+            with torch.no_grad(), self._amp():
+                return module(x)
+        key = (tuple(x.shape), x.dtype, x.stride())
+        entry = self._teacher_graphs.get(key)
+        if entry is None or entry[0] < 2:           # two eager calls first (library autotuning, lazy inits)
+            self._teacher_graphs[key] = (0 if entry is None else entry[0] + 1, None, None, None)
+            with torch.no_grad(), self._amp():
+                return module(x)
+        if entry[1] is None:
+            static_in = x.clone()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.current_stream().synchronize()
+            with torch.cuda.graph(graph):
+                with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=self.autocast,
+                                                     cache_enabled=False):
+                    static_out = module(static_in)
+            if not isinstance(static_out, torch.Tensor):
+                self._teacher_graphs[key] = (-10 ** 9, None, None, None)      # pytree outputs: stay eager
+                with torch.no_grad(), self._amp():
+                    return module(x)
+            entry = (2, graph, static_in, static_out)
+            self._teacher_graphs[key] = entry
+            # the capture itself did not execute anything: fall through to a replay
+        _, graph, static_in, static_out = entry
+        static_in.copy_(x)
+        graph.replay()
+        return static_out.clone()
 
     def _send_forward(self, op: Op, teacher: bool, outs: List[Any]) -> None:
         net = self._net(teacher)
