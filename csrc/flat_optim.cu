@@ -122,7 +122,32 @@ __global__ void __launch_bounds__(kThreads) lars_apply_kernel(float* __restrict_
   }
   const float wd_eff = adapt ? wd : 0.f;
   const float om = 1.f - ema_m;
-  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+  const bool has_t = teacher != nullptr;
+  // 16-byte vectors over the aligned body (segments start on 256-byte boundaries), scalars for the tail
+  const int n4 = ((c.begin & 3) == 0) ? (c.len >> 2) : 0;
+  float4* p4 = reinterpret_cast<float4*>(p + c.begin);
+  const float4* g4 = reinterpret_cast<const float4*>(g + c.begin);
+  float4* m4 = reinterpret_cast<float4*>(mu + c.begin);
+  float4* t4 = has_t ? reinterpret_cast<float4*>(teacher + c.begin) : nullptr;
+  for (int i = threadIdx.x; i < n4; i += kThreads) {
+    float4 pv = p4[i], mv = m4[i];
+    const float4 gv = g4[i];
+    const bool t_ok = has_t && (c.begin + 4 * (int64_t)i + 3 < teacher_n);
+    float4 tv = t_ok ? t4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#define TSP_LARS1(X)                                                   \
+    {                                                                  \
+      const float dp = q * (grad_scale * gv.X + wd_eff * pv.X);        \
+      mv.X = mom * mv.X + dp;                                          \
+      pv.X -= lr * mv.X;                                               \
+      tv.X = ema_m * tv.X + om * pv.X;                                 \
+    }
+    TSP_LARS1(x) TSP_LARS1(y) TSP_LARS1(z) TSP_LARS1(w)
+#undef TSP_LARS1
+    p4[i] = pv;
+    m4[i] = mv;
+    if (t_ok) t4[i] = tv;
+  }
+  for (int i = (n4 << 2) + threadIdx.x; i < c.len; i += kThreads) {
     const int64_t k = c.begin + i;
     const float pv = p[k];
     const float dp = q * (grad_scale * g[k] + wd_eff * pv);
@@ -130,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) lars_apply_kernel(float* __restrict_
     mu[k] = m2;
     const float np = pv - lr * m2;
     p[k] = np;
-    if (teacher != nullptr && k < teacher_n) teacher[k] = ema_m * teacher[k] + om * np;
+    if (has_t && k < teacher_n) teacher[k] = ema_m * teacher[k] + om * np;
   }
 }
 

@@ -122,14 +122,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+constexpr int kMaxBSources = 8;
+struct BMaps {
+  CUtensorMap m[kMaxBSources];
+};
+
 // Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulator
 // buffers in TMEM let the epilogue of tile i run while the MMAs of tile i+1 are issued; the smem ring keeps
 // streaming across tile boundaries.
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
-                    int* __restrict__ status) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ BMaps bmaps,
+                    int rows_per_b, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc,
+                    int epi, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   using C = Cfg<BN>;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -156,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&bmaps.m[0]) : "memory");
   }
   if (warp == 1) {        // one full warp allocates both accumulator buffers
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -184,7 +189,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           uint8_t* b_dst = a_dst + C::kABytes;
           mbar_expect_tx(full_bar + s, (uint32_t)C::kStageBytes);
           tma_load_2d(a_dst, &tmap_a, full_bar + s, kb * BK, m0);
-          tma_load_2d(b_dst, &tmap_b, full_bar + s, kb * BK, n0);
+          // B may be the row-wise concatenation of several buffers (one per GPU): tile rows n0.. live in
+          // source n0 / rows_per_b, which this CTA reads with its own TMA load (local or peer memory alike)
+          const int src = n0 / rows_per_b;
+          tma_load_2d(b_dst, &bmaps.m[src], full_bar + s, kb * BK, n0 - src * rows_per_b);
         }
       }
     }
@@ -312,10 +320,16 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int
 }
 
 template <int BN, typename OutT>
-int launch(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
-           int epi, int* status, cudaStream_t stream) {
-  CUtensorMap ta, tb;
-  if (!make_map(&ta, a, m, k, lda, BM) || !make_map(&tb, b, n, k, ldb, BN)) return -6;
+int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, const float* bias, int m, int n,
+           int k, int lda, int ldb, int ldc, int epi, int* status, cudaStream_t stream) {
+  CUtensorMap ta;
+  BMaps tb;
+  if (!make_map(&ta, a, m, k, lda, BM)) return -6;
+  for (int i = 0; i < kMaxBSources; ++i) {
+    const int src = i < n_src ? i : 0;
+    const int rows = n_src == 1 ? n : rows_per_b;
+    if (!make_map(&tb.m[i], b_srcs[src], rows, k, ldb, BN)) return -6;
+  }
   auto kern = gemm_tcgen05_kernel<BN, OutT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -332,7 +346,8 @@ int launch(const void* a, const void* b, void* c, const float* bias, int m, int 
   }
   const int num_tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
   const int grid = num_tiles < n_sm ? num_tiles : n_sm;
-  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, (OutT*)c, bias, m, n, k, ldc, epi, status);
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, n_src == 1 ? n + BN : rows_per_b, (OutT*)c, bias, m, n,
+                                                        k, ldc, epi, status);
   return TSP_LAUNCH_CHECK();
 }
 
@@ -351,12 +366,35 @@ int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, i
   if ((lda % 8) || (ldb % 8) || (k % 8)) return -3;
   if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
   if (epi != 0 && bias == nullptr) return -3;
+  void* srcs[1] = {const_cast<void*>(b)};
   const bool wide = n >= 256;
   if (out_dtype == TSP_DTYPE_BF16)
-    return wide ? launch<256, __nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
-                : launch<128, __nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
-  return wide ? launch<256, float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
-              : launch<128, float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+    return wide ? launch<256, __nv_bfloat16>(a, srcs, 1, n, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
+                : launch<128, __nv_bfloat16>(a, srcs, 1, n, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+  return wide ? launch<256, float>(a, srcs, 1, n, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream)
+              : launch<128, float>(a, srcs, 1, n, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+}
+
+// Same product with B given as `n_src` equally sized row blocks [rows_per_b, k] that may live on different GPUs
+// (peer-mapped pointers): C[:, r*rows_per_b : (r+1)*rows_per_b] = A * B_r^T.  This is the all-gather of the
+// MoCo keys folded into the contrastive-logit GEMM: every CTA pulls the key tile it needs straight from the owning
+// GPU with an ordinary (single-destination) TMA load.  rows_per_b must be a multiple of the N tile (256, or 128
+// when the total is below 256).
+int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, int m, int k,
+                                int lda, int ldb, int ldc, int out_dtype, int* status, cudaStream_t stream) {
+  if (m <= 0 || n_src <= 0 || rows_per_b <= 0 || k <= 0) return 0;
+  if (n_src > kMaxBSources) return -3;
+  if ((lda % 8) || (ldb % 8) || (k % 8)) return -3;
+  const int n = n_src * rows_per_b;
+  const bool wide = n >= 256 && rows_per_b % 256 == 0;
+  if (!wide && rows_per_b % 128 != 0) return -3;
+  for (int i = 0; i < n_src; ++i)
+    if ((uintptr_t)b_srcs[i] & 15) return -2;
+  if (out_dtype == TSP_DTYPE_BF16)
+    return wide ? launch<256, __nv_bfloat16>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream)
+                : launch<128, __nv_bfloat16>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream);
+  return wide ? launch<256, float>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream)
+              : launch<128, float>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream);
 }
 
 }  // extern "C"

@@ -217,8 +217,8 @@ int tsp_layernorm_fwd(const void* x, const float* w, const float* b, void* y, fl
 }
 
 int tsp_layernorm_bwd_blocks(int rows) {
-  int nb = (rows + 63) / 64;
-  const int cap = 148 * 4;
+  int nb = (rows + 15) / 16;            // >= 4 rows per warp; more blocks = more rows in flight
+  const int cap = 148 * 12;
   return nb > cap ? cap : (nb < 1 ? 1 : nb);
 }
 

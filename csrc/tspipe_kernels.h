@@ -78,6 +78,8 @@ int tsp_maxpool3x3s2_bwd(const void* dy, const uint8_t* idx, void* dx, int n, in
 // ---- gemm_tcgen05.cu ------------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,
                      int ldc, int out_dtype, int epi, int* status, cudaStream_t stream);
+int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, int m, int k,
+                                int lda, int ldb, int ldc, int out_dtype, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -75,6 +75,11 @@ def moco_loss(online_view_1, online_view_2, target_view_1, target_view_2, args=N
     (`benchmarks/moco-v3/moco/builder.py:73-85`)."""
     from .parallel.keys import gather_keys
     T = float(getattr(extra_args, "moco_t", 0.2))
+    if _fused_ok(online_view_1, target_view_2) and not getattr(extra_args, "no_fused", False):
+        from .ops import gemm
+        l1 = gemm.info_nce_replicas(online_view_1, target_view_2, T)
+        if l1 is not None:
+            return l1 + gemm.info_nce_replicas(online_view_2, target_view_1, T)
     k2, off = gather_keys(target_view_2)
     k1, _ = gather_keys(target_view_1)
     if _fused_ok(online_view_1, target_view_2) and not getattr(extra_args, "no_fused", False):

@@ -114,6 +114,61 @@ def info_nce(q: torch.Tensor, k: torch.Tensor, temp: float, k_all: Optional[torc
     return F.cross_entropy(logits, labels) * (2 * temp)
 
 
+def matmul_nt_gathered(a: torch.Tensor, b_sources, rows_per_b: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``a [M, K] @ concat(b_sources)^T`` where every source is a ``[rows_per_b, K]`` bf16 buffer that may live on
+    another GPU (peer-mapped): each CTA pulls its key tile from the owning GPU with its own TMA load."""
+    from ..comm.peer import pointer_table
+    a = a if (a.dtype == torch.bfloat16 and a.is_contiguous()) else a.to(torch.bfloat16).contiguous()
+    m, k = a.shape
+    r = len(b_sources)
+    c = torch.empty(m, r * rows_per_b, dtype=out_dtype, device=a.device)
+    L = _f.lib()
+    L.tsp_gemm_bf16_tn_gathered_b.restype = _c.c_int
+    with torch.cuda.device(a.device):
+        code = L.tsp_gemm_bf16_tn_gathered_b(_f._ptr(a), pointer_table(b_sources), _c.c_int(r), _c.c_int(rows_per_b),
+                                             _f._ptr(c), _c.c_int(m), _c.c_int(k), _c.c_int(k), _c.c_int(k),
+                                             _c.c_int(r * rows_per_b), _c.c_int(_f._dt(c)),
+                                             _f._ptr(_status_word(a.device)), _f._stream())
+    _f._check(code, "tsp_gemm_bf16_tn_gathered_b")
+    _f._count()
+    return c
+
+
+class _GatheredLogits(torch.autograd.Function):
+    """Contrastive logits against the keys of ALL replicas, read in place from the GPUs that own them."""
+
+    @staticmethod
+    def forward(ctx, qn, views, table, rows_per_b, like):
+        ctx.table, ctx.r, ctx.like, ctx.adtype = table, len(views), like, qn.dtype
+        return matmul_nt_gathered(qn, views, rows_per_b)
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..parallel.keys import gather_blocks
+        k_all = gather_blocks(ctx.table, ctx.r, ctx.like)           # [R*n, D] (already scaled by 1/T)
+        return matmul_nt(g, k_all.t().contiguous(), out_dtype=torch.float32).to(ctx.adtype), None, None, None, None
+
+
+def info_nce_replicas(q: torch.Tensor, k: torch.Tensor, temp: float):
+    """InfoNCE across data-parallel replicas with the key all-gather folded into the logit GEMM.  Returns None
+    when the fused path does not apply (no replicas, CPU, shapes off the tile grid)."""
+    from ..parallel.keys import exchange_for
+    from ..runtime import context
+    ctx = context.current()
+    n, d = q.shape
+    if ctx is None or ctx.topo.dp <= 1 or not q.is_cuda or d % 8 or d < 64 or n % 128:
+        return None
+    kn = (F.normalize(k.detach().float(), dim=1) * (1.0 / temp)).to(torch.bfloat16).contiguous()
+    ex = exchange_for(kn, "moco_keys_scaled_bf16")
+    if ex is None:
+        return None
+    views, table = ex.publish(kn)
+    qn = F.normalize(q.float(), dim=1)
+    logits = _GatheredLogits.apply(qn, views, table, n, kn)
+    labels = torch.arange(n, device=q.device) + n * ctx.topo.replica
+    return _f.cross_entropy(logits, labels) * (2 * temp)
+
+
 class _ScaledLogits(torch.autograd.Function):
     """``scale * a @ b^T`` in fp32 on the tcgen05 kernel; gradient w.r.t. ``a`` only."""
 

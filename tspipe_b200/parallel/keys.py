@@ -21,6 +21,51 @@ import torch.distributed as dist
 from ..runtime import context
 
 
+class KeyExchange:
+    """Two peer-mapped slots per rank for one (shape, dtype) of keys; :meth:`publish` writes this step's
+    keys into the slot of the step's parity and returns every replica's slot of that parity once a
+    stream-ordered collective has established that all of them are written."""
+
+    def __init__(self, like: torch.Tensor, topo):
+        from ..comm import peer
+        self.topo = topo
+        self.slots = [torch.zeros_like(like) for _ in range(2)]
+        self.views = [peer.exchange(s, topo.dp_group, topo.dp_ranks) for s in self.slots]
+        self.tables = [peer.pointer_table(v) for v in self.views]
+        self.token = torch.zeros(1, device=like.device)
+        self.step = 0
+
+    def publish(self, k: torch.Tensor):
+        par = self.step & 1
+        self.step += 1
+        self.slots[par].copy_(k)
+        dist.all_reduce(self.token, group=self.topo.dp_group)     # all replicas' keys of this step are in place
+        return self.views[par], self.tables[par]
+
+
+def exchange_for(k: torch.Tensor, tag: str) -> Optional[KeyExchange]:
+    ctx = context.current()
+    if ctx is None or ctx.topo.dp <= 1 or not (k.is_cuda and ctx.peer_memory and ctx.fused):
+        return None
+    key = (tag, tuple(k.shape), k.dtype)
+    if key not in ctx.cache:
+        ctx.cache[key] = KeyExchange(k, ctx.topo)
+    return ctx.cache[key]
+
+
+def gather_blocks(table, n_peers: int, like: torch.Tensor) -> torch.Tensor:
+    """Concatenate every replica's block (read with peer loads) into a local ``[R*n, ...]`` tensor."""
+    from ..ops import fused
+    out = torch.empty((n_peers * like.shape[0],) + tuple(like.shape[1:]), dtype=like.dtype, device=like.device)
+    L = fused.lib()
+    L.tsp_gather_blocks.restype = ctypes.c_int
+    with torch.cuda.device(like.device):
+        fused._check(L.tsp_gather_blocks(table, ctypes.c_int(n_peers), ctypes.c_int64(like.numel() * like.element_size()),
+                                         fused._ptr(out), fused._stream()), "tsp_gather_blocks")
+    fused._count()
+    return out
+
+
 def gather_keys(k: torch.Tensor) -> Tuple[torch.Tensor, int]:
     """``(k_all [N, D], label_offset)`` for the replica this rank belongs to; identity without replicas."""
     ctx = context.current()
@@ -29,29 +74,10 @@ def gather_keys(k: torch.Tensor) -> Tuple[torch.Tensor, int]:
     topo = ctx.topo
     n = k.shape[0]
     k = k.detach().contiguous()
-    if not (k.is_cuda and ctx.peer_memory and ctx.fused and (k.numel() * k.element_size()) % 16 == 0):
+    ex = exchange_for(k, "moco_keys") if (k.numel() * k.element_size()) % 16 == 0 else None
+    if ex is None:
         parts = [torch.empty_like(k) for _ in range(topo.dp)]
         dist.all_gather(parts, k, group=topo.dp_group)
         return torch.cat(parts), n * topo.replica
-    from ..comm import peer
-    from ..ops import fused
-    key = ("moco_keys", tuple(k.shape), k.dtype)
-    st = ctx.cache.get(key)
-    if st is None:
-        slots = [torch.zeros_like(k) for _ in range(2)]
-        views = [peer.exchange(s, topo.dp_group, topo.dp_ranks) for s in slots]
-        st = ctx.cache[key] = dict(slots=slots, tables=[peer.pointer_table(v) for v in views], keep=views, step=0,
-                                   token=torch.zeros(1, device=k.device))
-    par = st["step"] & 1
-    st["step"] += 1
-    st["slots"][par].copy_(k)
-    dist.all_reduce(st["token"], group=topo.dp_group)         # all replicas' keys of this step are in place
-    out = torch.empty((topo.dp * n,) + tuple(k.shape[1:]), dtype=k.dtype, device=k.device)
-    L = fused.lib()
-    L.tsp_gather_blocks.restype = ctypes.c_int
-    with torch.cuda.device(k.device):
-        fused._check(L.tsp_gather_blocks(st["tables"][par], ctypes.c_int(topo.dp),
-                                         ctypes.c_int64(k.numel() * k.element_size()), fused._ptr(out),
-                                         fused._stream()), "tsp_gather_blocks")
-    fused._count()
-    return out, n * topo.replica
+    _, table = ex.publish(k)
+    return gather_blocks(table, topo.dp, k), n * topo.replica
