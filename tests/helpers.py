@@ -14,25 +14,30 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, ret):
+def _entry(rank, world, port, fn, args, ret, hard_exit=False):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.set_num_threads(1)
     try:
         ret[rank] = fn(rank, world, *args)
+        if hard_exit:
+            # the rank may still own threads blocked in a collective that will never complete (that is what
+            # the test provokes); leave without running their destructors
+            sys.stdout.flush()
+            os._exit(0)
     except BaseException:
         ret[rank] = ("__error__", traceback.format_exc())
         raise
 
 
-def run_ranks(fn, world, *args, timeout=240):
+def run_ranks(fn, world, *args, timeout=240, hard_exit=False):
     """Run ``fn(rank, world, *args)`` in ``world`` spawned processes (launcher-style env) and return
     the list of their return values."""
     ctx = mp.get_context("spawn")
     mgr = ctx.Manager()
     ret = mgr.dict()
     port = free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, ret, hard_exit)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

@@ -90,7 +90,7 @@ def _rank(rank, world):
 def test_executor_exception_on_one_rank_stops_all_ranks():
     """The loss stage (rank 1) raises at batch 3; rank 0 learns about it from the store and raises from
     ``feed`` within a few heartbeats instead of blocking on its gradient receive."""
-    out = run_ranks(_rank, 2, timeout=90)
+    out = run_ranks(_rank, 2, timeout=90, hard_exit=True)
     assert out[1][0] == "failed" and "injected failure" in out[1][2]
     assert out[0][0] == "failed" and ("rank 1 failed" in out[0][2] or "peer" in out[0][2])
     assert out[0][1] < 15 and out[1][1] < 15
