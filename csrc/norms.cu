@@ -139,6 +139,99 @@ __global__ void __launch_bounds__(128) ln_bwd_kernel(const T* __restrict__ dy, c
   for (int i = threadIdx.x; i < 2 * d; i += blockDim.x) out[i] = sm[i];
 }
 
+// LayerNorm backward, split form: (a) dx only - one warp per row, no cross-row state, high occupancy;
+// (b) dw/db as a column reduction over rows: thread = 8 columns, block = a contiguous range of rows, per-block
+// partial sums to `partial` ([gridDim.x][2][d]), reduced by ln_bwd_reduce_kernel.
+template <typename T>
+__global__ void __launch_bounds__(128) ln_bwd_dx_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                        const float* __restrict__ w, const float* __restrict__ mean,
+                                                        const float* __restrict__ rstd, T* __restrict__ dx, int rows,
+                                                        int d) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= rows) return;
+  const int nvec = d >> 3;
+  const T* xr = x + (int64_t)row * d;
+  const T* gr = dy + (int64_t)row * d;
+  T* dr = dx + (int64_t)row * d;
+  const float mu = mean[row], rs = rstd[row];
+  float xh[kLnMaxVec][8], gw[kLnMaxVec][8];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+      float xv[8], gv[8], wv[8];
+      tsp::ld8(xr, (int64_t)vi * 8, xv);
+      tsp::ld8(gr, (int64_t)vi * 8, gv);
+      tsp::ld8(w, (int64_t)vi * 8, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        xh[k][e] = (xv[e] - mu) * rs;
+        gw[k][e] = gv[e] * wv[e];
+        s1 += gw[k][e];
+        s2 += gw[k][e] * xh[k][e];
+      }
+    }
+  }
+  s1 = tsp::warp_sum(s1) / d;
+  s2 = tsp::warp_sum(s2) / d;
+#pragma unroll
+  for (int k = 0; k < kLnMaxVec; ++k) {
+    const int vi = lane + 32 * k;
+    if (vi < nvec) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rs * (gw[k][e] - s1 - xh[k][e] * s2);
+      tsp::st8(dr, (int64_t)vi * 8, o);
+    }
+  }
+}
+
+// block = (d/8 column vectors) x (256 / (d/8) rows in parallel); dynamic smem = threads * 16 floats
+template <typename T>
+__global__ void __launch_bounds__(256) ln_bwd_colsum_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                                            const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd,
+                                                            float* __restrict__ partial, int rows, int d) {
+  extern __shared__ float sm[];
+  const int nvec = d >> 3;
+  const int tx_n = nvec < 256 ? nvec : 256;
+  const int ty_n = 256 / tx_n;
+  const int tx = threadIdx.x % tx_n, ty = threadIdx.x / tx_n;
+  const bool active = ty < ty_n && tx < nvec;
+  float a[8], b[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { a[e] = 0.f; b[e] = 0.f; }
+  if (active) {
+    const int rows_per_block = (rows + gridDim.x - 1) / gridDim.x;
+    const int r0 = blockIdx.x * rows_per_block;
+    const int r1 = min(rows, r0 + rows_per_block);
+    for (int r = r0 + ty; r < r1; r += ty_n) {
+      float gv[8], xv[8];
+      tsp::ld8(dy, (int64_t)r * d + tx * 8, gv);
+      tsp::ld8(x, (int64_t)r * d + tx * 8, xv);
+      const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[e] += gv[e] * (xv[e] - mu) * rs; b[e] += gv[e]; }
+    }
+  }
+  float* mine = sm + (int64_t)threadIdx.x * 16;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { mine[e] = a[e]; mine[8 + e] = b[e]; }
+  __syncthreads();
+  if (ty == 0 && tx < nvec) {
+    for (int k = 1; k < ty_n; ++k) {
+      const float* o = sm + (int64_t)(k * tx_n + tx) * 16;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[e] += o[e]; b[e] += o[8 + e]; }
+    }
+    float* out = partial + (int64_t)blockIdx.x * 2 * d;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { out[tx * 8 + e] = a[e]; out[d + tx * 8 + e] = b[e]; }
+  }
+}
+
 // part 2: dw[j] = sum_blocks partial[b][0][j], db likewise.
 __global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restrict__ partial, int nblocks, int d,
                                                             float* __restrict__ dw, float* __restrict__ db) {
@@ -217,8 +310,8 @@ int tsp_layernorm_fwd(const void* x, const float* w, const float* b, void* y, fl
 }
 
 int tsp_layernorm_bwd_blocks(int rows) {
-  int nb = (rows + 15) / 16;            // >= 4 rows per warp; more blocks = more rows in flight
-  const int cap = 148 * 12;
+  int nb = (rows + 63) / 64;
+  const int cap = 148 * 4;
   return nb > cap ? cap : (nb < 1 ? 1 : nb);
 }
 
@@ -228,14 +321,19 @@ int tsp_layernorm_bwd(const void* dy, const void* x, const float* w, const float
   if (rows <= 0) return 0;
   if (d % 8 != 0 || d > 8 * 32 * kLnMaxVec) return -3;
   const int nb = tsp_layernorm_bwd_blocks(rows);
-  const int rpb = (rows + nb - 1) / nb;
-  const size_t smem = sizeof(float) * 2 * (size_t)d;
-  if (dtype == TSP_DTYPE_BF16)
-    ln_bwd_kernel<__nv_bfloat16><<<nb, 128, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w, mean,
-                                                            rstd, (__nv_bfloat16*)dx, partial, rows, d, rpb);
-  else
-    ln_bwd_kernel<float><<<nb, 128, smem, stream>>>((const float*)dy, (const float*)x, w, mean, rstd, (float*)dx,
-                                                    partial, rows, d, rpb);
+  const int grid_dx = (rows + 3) / 4;
+  const size_t smem = sizeof(float) * 16 * 256;
+  if (dtype == TSP_DTYPE_BF16) {
+    ln_bwd_dx_kernel<__nv_bfloat16><<<grid_dx, 128, 0, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, w,
+                                                                 mean, rstd, (__nv_bfloat16*)dx, rows, d);
+    ln_bwd_colsum_kernel<__nv_bfloat16><<<nb, 256, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                   mean, rstd, partial, rows, d);
+  } else {
+    ln_bwd_dx_kernel<float><<<grid_dx, 128, 0, stream>>>((const float*)dy, (const float*)x, w, mean, rstd, (float*)dx,
+                                                         rows, d);
+    ln_bwd_colsum_kernel<float><<<nb, 256, smem, stream>>>((const float*)dy, (const float*)x, mean, rstd, partial, rows,
+                                                           d);
+  }
   ln_bwd_reduce_kernel<<<(2 * d + 255) / 256, 256, 0, stream>>>(partial, nb, d, dw, db);
   return TSP_LAUNCH_CHECK();
 }

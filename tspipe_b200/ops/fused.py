@@ -297,7 +297,7 @@ class _LayerNorm(torch.autograd.Function):
             _check(lib().tsp_layernorm_bwd(_ptr(dy2), _ptr(x2), _ptr(wf), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(dw),
                                            _ptr(db), _ptr(partial), _c.c_int(rows), _c.c_int(d), _c.c_int(_dt(x2)),
                                            _stream()), "tsp_layernorm_bwd")
-        _count(2)
+        _count(3)
         return dx.view(ctx.shape), dw.to(ctx.wdtype), db.to(ctx.wdtype), None
 
 
