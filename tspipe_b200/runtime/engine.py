@@ -26,7 +26,7 @@ import queue
 import threading
 import time
 import traceback
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -37,7 +37,6 @@ from ..batch_ops import Batch, ScatterGatherFn, defaultScatterGatherFn
 from ..comm.links import Link, MetaBoard, RecvHandle
 from ..comm.topology import Topology
 from ..logger import Log
-from ..model_wrapper import TSPipeModelOutput
 from ..schedule import Op, OpKind, ScheduleSpec, batch_block
 from ..utils import pytree as pt
 from .state import FlatParams, corresponding_prefix
@@ -208,8 +207,7 @@ class StageEngine:
                  loss_fn: Callable, target_update_fn: Optional[Callable], momentum: float,
                  kd_mode: bool, target_train_mode: bool = True,
                  scatter_gather_fn: ScatterGatherFn = defaultScatterGatherFn,
-                 args: Any = None, extra_args: Any = None, inbox=None, loss_sink: Optional[Callable] = None,
-                 profiler=None, ema_plan=None):
+                 args: Any = None, extra_args: Any = None, inbox=None, profiler=None, ema_plan=None):
         self.topo, self.cfg = topo, config
         self.device = topo.device
         self.cuda = topo.is_cuda
@@ -219,7 +217,6 @@ class StageEngine:
         self.sg = scatter_gather_fn
         self.args, self.extra_args = args, extra_args
         self.inbox = inbox if inbox is not None else queue.Queue()
-        self.loss_sink = loss_sink
         self.profiler = profiler
         rt = config["runtime"]
         gp = config["gpipe_emulation"]
@@ -302,7 +299,6 @@ class StageEngine:
         self.error: Optional[BaseException] = None
         self.thread: Optional[threading.Thread] = None
         self.losses: "queue.Queue[Tuple[int, Any]]" = queue.Queue()
-        self._pending_loss: List[Tuple[int, torch.Tensor, Any]] = []
         self.op_count = 0
         self.on_batch_done: Optional[Callable[[int], None]] = None
         self.on_idle: Optional[Callable[[], None]] = None

@@ -18,23 +18,19 @@ a different runtime:
 """
 from __future__ import annotations
 
-import copy
 import os
 import queue
-import sys
 import time
 import warnings
 from argparse import Namespace
 from collections import OrderedDict
 from enum import Enum
-from itertools import chain
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist
 from torch import nn
 
-from . import batch_ops
 from .batch_ops import Batch, BatchQueue, ScatterGatherFn, defaultScatterGatherFn
 from .batchnorm import DeferredBatchNorm
 from .config import load_yaml, merge_config, parse_cli
