@@ -112,12 +112,15 @@ class ScheduleSpec:
     def teacher_head(self, stage: int) -> int:
         """Number of next-batch teacher forwards placed *before* the backward wave.
 
-        The wave needs ``n-1-j`` hops down and ``n-1-j`` hops back after stage ``j``
-        finishes its last student forward, so ``2(n-1-j)`` unit slots are free.  In
+        After stage ``j`` finishes its last student forward the wave needs ``n-1-j``
+        forward hops down (one slot each) and ``n-1-j`` backward hops back, a backward
+        item costing ``2 / bwd_split`` forward slots: with the reference's split of 2
+        that is ``2(n-1-j)`` free slots, with unsplit backwards ``3(n-1-j)``.  In
         the SSL table the slots are consecutive teacher items; under the KD filter
         the dropped view-0 items come first, so only the view-1 part survives.
         """
-        free = 2 * (self.n_stages - 1 - stage)
+        hops = self.n_stages - 1 - stage
+        free = hops + (2 * hops + self.bwd_split - 1) // self.bwd_split
         full = 2 * self.n_ubatch
         head_ssl = min(free, full)
         if not self.kd:
