@@ -55,7 +55,7 @@ def run_reference(a) -> None:
     env["CUDA_VISIBLE_DEVICES"] = ",".join(str(i) for i in range(a.gpus))
     cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(a.gpus), "--steps", str(a.steps),
            "--warmup", str(a.warmup), "--per-gpu-batch", str(a.per_gpu_batch)]
-    limit = int(os.environ.get("TSPIPE_REF_TIMEOUT", 900))
+    limit = int(os.environ.get("TSPIPE_REF_TIMEOUT", 600))
     import signal
     proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
                             start_new_session=True)
