@@ -6,6 +6,7 @@
     python benchmarks/kernel_cases.py kd        # soft-target KD loss on [2048, 1000] logits
     python benchmarks/kernel_cases.py ln        # LayerNorm fwd/bwd on [512*197, 768]
     python benchmarks/kernel_cases.py gemm      # tcgen05 GEMM 8192 x 3072 x 768
+    python benchmarks/kernel_cases.py infonce   # MoCo InfoNCE forward + backward, 4096 x 256
 
 Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2 where DRAM figures
 matter), runs the op a handful of times and prints CUDA-event timings with the achieved bandwidth.
@@ -119,5 +120,29 @@ def case_gemm():
     print(f"tcgen05 gemm {m}x{n}x{k}: {t:8.1f} us  {2 * m * n * k / t / 1e6:7.1f} TFLOP/s   (library: {tr:8.1f} us)")
 
 
+def case_infonce():
+    import torch.nn.functional as F
+    from tspipe_b200.ops import fused, gemm
+    dev = torch.device("cuda")
+    n, d, temp = 4096, 256, 0.2
+    q = torch.randn(n, d, device=dev, requires_grad=True)
+    k = torch.randn(n, d, device=dev)
+
+    def ours():
+        q.grad = None
+        fused.info_nce_loss(q, k, temp).backward()
+
+    def ref():
+        q.grad = None
+        logits = F.normalize(q, dim=1) @ F.normalize(k, dim=1).t() / temp
+        (F.cross_entropy(logits, torch.arange(n, device=dev)) * 2 * temp).backward()
+
+    t, tr = _time(ours, n=10), _time(ref, n=10)
+    gemm.check_status()
+    flops = 2 * 2 * n * n * d          # logits + dq
+    print(f"info_nce fwd+bwd [{n},{d}]: {t:8.1f} us  ({flops / t / 1e6:6.1f} TFLOP/s on the two GEMMs)   library ops: {tr:8.1f} us")
+
+
 if __name__ == "__main__":
-    {"bn": case_bn, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm}[sys.argv[1]]()
+    {"bn": case_bn, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
+     "infonce": case_infonce}[sys.argv[1]]()

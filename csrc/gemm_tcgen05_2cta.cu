@@ -1,0 +1,379 @@
+// bf16 GEMM with two SMs per output tile: C[M,N] = A[M,K] * B[N,K]^T, fp32 accumulation, 256 x 256 tiles.
+//
+// A cluster of two CTAs owns one 256 x 256 tile.  CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and
+// rows [128 r, 128 r + 128) of the B tile (half of N) with its own TMA loads; the leader CTA (rank 0) issues
+// tcgen05.mma.cta_group::2, which reads A from both CTAs' shared memory and the two halves of B, and writes each
+// CTA's 128 x 256 accumulator slice into that CTA's tensor memory.  Compared with the one-CTA kernel
+// (gemm_tcgen05.cu: 48 KB of operands per 128 x 256 x 64 step) each SM moves 32 KB per step for the same FLOPs.
+//
+// Synchronisation (all mbarriers; every wait bounded, see mbar_wait):
+//   full[s]        in the leader: armed by the leader's producer with the bytes of BOTH CTAs; every TMA load of the
+//                  pair completes its bytes on the leader's barrier (cp.async.bulk.tensor ... .cta_group::2);
+//   empty[s]       in each CTA: the leader commits the MMAs that read slot s to its own and to the peer's barrier;
+//   tmem_full[a]   in each CTA: committed by the leader after the last MMA of a tile;
+//   tmem_empty[a]  in the leader: 8 arrivals, one per epilogue warp of the pair (the peer's arrive remotely).
+// The cluster is synchronised once after barrier initialisation and once before exit, so no CTA leaves while its
+// partner can still touch its shared memory.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tspipe_kernels.h"
+
+namespace {
+
+constexpr int BM = 128;          // rows per CTA (pair tile: 256)
+constexpr int BN = 256;          // tile columns; each CTA stages BN / 2 rows of B
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 6;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = (BN / 2) * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;                  // per CTA
+constexpr int kTmemCols = 2 * BN;                               // two accumulator buffers
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(local_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*((volatile int*)status) != 0) return false;
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+// TMA load into this CTA's shared memory whose byte count completes on a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(map), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+  return d;
+}
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on a barrier (any CTA of the cluster) once all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
+                         int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(tiles + kStages * kStageBytes);
+  uint64_t* full_bar = bars;                           // [kStages]  used in the leader only
+  uint64_t* empty_bar = bars + kStages;                // [kStages]  in each CTA
+  uint64_t* tmem_full_bar = bars + 2 * kStages;        // [2]        in each CTA
+  uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;   // [2]        used in the leader only
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * kStages + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_m = (m + 2 * BM - 1) / (2 * BM), tiles_n = (n + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar + s, 1);
+      mbar_init(empty_bar + s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar + a, 1);
+      mbar_init(tmem_empty_bar + a, 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+  }
+  if (warp == 1) {        // warp 1 of BOTH CTAs: paired allocation of both accumulator buffers
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                   // both CTAs' barriers exist before anyone signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one thread per CTA) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM;
+        const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1)) { ok = false; break; }
+          uint8_t* a_dst = tiles + s * kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          if (leader) mbar_expect_tx(full_bar + s, 2u * (uint32_t)kStageBytes);
+          const uint32_t lbar = map_to_cta(smem_u32(full_bar + s), 0);
+          tma_load_2d_pair(a_dst, &tmap_a, lbar, kb * BK, m0);
+          tma_load_2d_pair(b_dst, &tmap_b, lbar, kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
+        const uint32_t acc = lt & 1, use = lt >> 1;
+        if (use > 0) {
+          ok = mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t round = it / kStages;
+          ok = mbar_wait(full_bar + s, round & 1, status, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
+          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_bf16_pair(d_tmem, a_desc + (uint64_t)(2 * kk), b_desc + (uint64_t)(2 * kk), idesc,
+                           (kb > 0 || kk > 0) ? 1u : 0u);
+          const uint32_t e_local = smem_u32(empty_bar + s);
+          umma_commit_pair(e_local);                       // slot s is free again in this CTA ...
+          umma_commit_pair(map_to_cta(e_local, 1));        // ... and in the partner
+        }
+        const uint32_t f_local = smem_u32(tmem_full_bar + acc);
+        umma_commit_pair(f_local);
+        umma_commit_pair(map_to_cta(f_local, 1));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs): this CTA's 128 rows, all BN columns ----------------
+    const int quarter = warp & 3;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
+      const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM, n0 = (t / tiles_m) * BN;
+      const uint32_t acc = lt & 1, use = lt >> 1;
+      ok = mbar_wait(tmem_full_bar + acc, use & 1, status, 3);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, r);
+        const int col = n0 + c0;
+        if (row < m && col < n) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (epi != 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] += (col + j < n) ? bias[col + j] : 0.f;
+              if (epi == 2) v[j] = gelu_erf(v[j]);
+            }
+          }
+          OutT* dst = c + (int64_t)row * ldc + col;
+          if (col + 32 <= n && ((ldc * (int)sizeof(OutT)) % 16 == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float t8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) t8[e] = v[j + e];
+              tsp::st8(dst, j, t8);
+            }
+          } else {
+            for (int j = 0; j < 32 && col + j < n; ++j) tsp::st(dst, j, v[j]);
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty_bar + acc), 0));
+    }
+  }
+  if (*((volatile int*)status) != 0) {
+    // a wait ran out somewhere: give TMA loads and MMAs that are still in flight time to land before the pair's
+    // shared memory and tensor memory are released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();                                   // nobody touches the partner's memory after this point
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename OutT>
+int launch(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
+           int epi, int* status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (!make_map(&ta, a, m, k, lda, BM) || !make_map(&tb, b, n, k, ldb, BN / 2)) return -6;
+  auto kern = gemm_tcgen05_2cta_kernel<OutT>;
+  static bool attr_set[64] = {};
+  static int n_sm[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm[dev] <= 0) n_sm[dev] = 148;
+    attr_set[dev] = true;
+  }
+  const int num_tiles = ((n + BN - 1) / BN) * ((m + 2 * BM - 1) / (2 * BM));
+  int pairs = n_sm[dev] / 2;
+  if (pairs > num_tiles) pairs = num_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, (OutT*)c, bias, m, n, k, ldc, epi, status);
+  return (int)e;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Two-SM variant of tsp_gemm_bf16_tn, same arguments: C[m,n] = A[m,k] * B[n,k]^T (+ bias[n]) (-> GELU), bf16
+// operands, C bf16 or fp32; epi 0 none, 1 bias, 2 bias + GELU.
+// `status`: one zeroed int in device memory; non-zero afterwards = a bounded wait ran out (1 producer, 2 MMA on
+// operands, 3 epilogue, 4 MMA on a free accumulator) and C is not valid.
+int tsp_gemm_bf16_tn_2cta(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda,
+                          int ldb, int ldc, int out_dtype, int epi, int* status, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (epi != 0 && bias == nullptr) return -3;
+  if ((lda % 8) || (ldb % 8) || (k % 8)) return -3;
+  if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
+  if (out_dtype == TSP_DTYPE_BF16) return launch<__nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+  return launch<float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+}
+
+}  // extern "C"

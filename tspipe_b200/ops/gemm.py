@@ -37,7 +37,7 @@ def check_status(device=None) -> None:
         if code != 0:
             t.zero_()
             raise RuntimeError(f"tcgen05 GEMM on {key}: bounded wait ran out in role {code} "
-                               "(1 = TMA producer, 2 = MMA issuer, 3 = epilogue)")
+                               "(1 = TMA producer, 2 = MMA issuer, 3 = epilogue, 4 = MMA issuer on a free accumulator)")
 
 
 def eligible(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -46,9 +46,19 @@ def eligible(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.numel() // k >= 128)
 
 
+_two_cta = False
+
+
+def set_two_cta(on: bool) -> None:
+    """Route :func:`matmul_nt` through the two-SM kernel (``cta_group::2``, one 256 x 256 tile per CTA pair)."""
+    global _two_cta
+    _two_cta = bool(on)
+
+
 def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
-              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """``a [M, K] @ b [N, K]^T`` (bf16 operands)."""
+              out_dtype: torch.dtype = torch.bfloat16, two_cta: Optional[bool] = None) -> torch.Tensor:
+    """``a [M, K] @ b [N, K]^T`` (bf16 operands).  ``two_cta`` picks the CTA-pair kernel for this call
+    (default: the module setting, see :func:`set_two_cta`)."""
     assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1]
     a = a if (a.dtype == torch.bfloat16 and a.is_contiguous()) else a.to(torch.bfloat16).contiguous()
     b = b if (b.dtype == torch.bfloat16 and b.is_contiguous()) else b.to(torch.bfloat16).contiguous()
@@ -60,11 +70,12 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = N
     if gelu and bias is None:
         bf, epi = torch.zeros(n, dtype=torch.float32, device=a.device), 2
     L = _f.lib()
-    L.tsp_gemm_bf16_tn.restype = _c.c_int
+    fn = L.tsp_gemm_bf16_tn_2cta if (_two_cta if two_cta is None else two_cta) else L.tsp_gemm_bf16_tn
+    fn.restype = _c.c_int
     with torch.cuda.device(a.device):
-        code = L.tsp_gemm_bf16_tn(_f._ptr(a), _f._ptr(b), _f._ptr(c), _f._ptr(bf), _c.c_int(m), _c.c_int(n), _c.c_int(k),
-                                  _c.c_int(k), _c.c_int(k), _c.c_int(n), _c.c_int(_f._dt(c)), _c.c_int(epi),
-                                  _f._ptr(_status_word(a.device)), _f._stream())
+        code = fn(_f._ptr(a), _f._ptr(b), _f._ptr(c), _f._ptr(bf), _c.c_int(m), _c.c_int(n), _c.c_int(k),
+                  _c.c_int(k), _c.c_int(k), _c.c_int(n), _c.c_int(_f._dt(c)), _c.c_int(epi),
+                  _f._ptr(_status_word(a.device)), _f._stream())
     _f._check(code, "tsp_gemm_bf16_tn")
     _f._count()
     return c
