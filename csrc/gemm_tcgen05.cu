@@ -269,7 +269,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               tsp::st8(dst, j, t8);
             }
           } else {
-            for (int j = 0; j < 32 && col + j < n; ++j) tsp::st(dst, j, v[j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)        // constant indices only: v stays in registers
+              if (col + j < n) tsp::st(dst, j, v[j]);
           }
         }
       }

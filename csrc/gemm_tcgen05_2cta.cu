@@ -12,6 +12,8 @@
 //   empty[s]       in each CTA: the leader commits the MMAs that read slot s to its own and to the peer's barrier;
 //   tmem_full[a]   in each CTA: committed by the leader after the last MMA of a tile;
 //   tmem_empty[a]  in the leader: 8 arrivals, one per epilogue warp of the pair (the peer's arrive remotely).
+// Epilogue: TMEM -> registers -> swizzled shared memory -> TMA store (32 rows x 128 bytes per store, two buffers
+// per warp); direct per-thread stores when C has no 16-byte-aligned base and row pitch.
 // The cluster is synchronised once after barrier initialisation and once before exit, so no CTA leaves while its
 // partner can still touch its shared memory.
 #include <cuda.h>
@@ -32,7 +34,9 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = (BN / 2) * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;                  // per CTA
 constexpr int kTmemCols = 2 * BN;                               // two accumulator buffers
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kStoreBufBytes = 32 * 128;                        // 32 rows x 128 bytes of C, one TMA store
+constexpr int kStoreBytes = 4 * 2 * kStoreBufBytes;             // two buffers per epilogue warp
+constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -113,7 +117,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -124,7 +128,20 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// TMA store of one 32-row x 128-byte block (128-byte swizzle) from shared memory; rows / columns beyond the
+// tensor's extent are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
@@ -132,11 +149,12 @@ __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + er
 template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
+                         const __grid_constant__ CUtensorMap tmap_c, int tma_store, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
                          int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(tiles + kStages * kStageBytes);
+  uint8_t* store_bufs = tiles + kStages * kStageBytes; // 1024-aligned: the swizzle pattern follows address bits
+  uint64_t* bars = (uint64_t*)(store_bufs + kStoreBytes);
   uint64_t* full_bar = bars;                           // [kStages]  used in the leader only
   uint64_t* empty_bar = bars + kStages;                // [kStages]  in each CTA
   uint64_t* tmem_full_bar = bars + 2 * kStages;        // [2]        in each CTA
@@ -234,8 +252,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   } else {
     // ---------------- epilogue (both CTAs): this CTA's 128 rows, all BN columns ----------------
+    // Per warp: 32 accumulator rows.  Blocks of 128 output bytes per row (64 bf16 or 32 fp32 columns) go
+    // TMEM -> registers -> (bias, GELU, convert) -> swizzled shared memory -> one TMA store; two staging
+    // buffers per warp, so the store of block i overlaps the conversion of block i + 1.  Without a usable
+    // tensor map for C (unaligned base or row pitch) every thread stores its own row directly.
+    constexpr int kCols = 128 / (int)sizeof(OutT);
     const int quarter = warp & 3;
-    uint32_t lt = 0;
+    uint8_t* my_bufs = store_bufs + quarter * 2 * kStoreBufBytes;
+    uint32_t lt = 0, nstore = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
       const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM, n0 = (t / tiles_m) * BN;
@@ -243,41 +267,70 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       ok = mbar_wait(tmem_full_bar + acc, use & 1, status, 3);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = m0 + quarter * 32 + lane;
+      const int row0 = m0 + quarter * 32, row = row0 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, r);
+      for (int c0 = 0; c0 < BN; c0 += kCols) {
+        float v[kCols];
+        {
+          uint32_t r[kCols];
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0;
+          tmem_ld_32x32_issue(taddr, r);
+          if constexpr (kCols == 64) tmem_ld_32x32_issue(taddr + 32, r + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) v[j] = __uint_as_float(r[j]);
+        }
         const int col = n0 + c0;
-        if (row < m && col < n) {
-          float v[32];
+        if (epi != 0 && col < n) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (epi != 0) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              v[j] += (col + j < n) ? bias[col + j] : 0.f;
-              if (epi == 2) v[j] = gelu_erf(v[j]);
-            }
+          for (int j = 0; j < kCols; ++j) {
+            v[j] += (col + j < n) ? bias[col + j] : 0.f;
+            if (epi == 2) v[j] = gelu_erf(v[j]);
           }
+        }
+        if (tma_store) {
+          uint8_t* buf = my_bufs + (nstore & 1) * kStoreBufBytes;
+          if (nstore >= 2) {         // the store issued two blocks ago has finished reading this buffer
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+          }
+          uint8_t* my_row = buf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {   // 16-byte piece j of this row sits at piece (j ^ (row & 7))
+            uint4 q;
+            if constexpr (kCols == 64) {
+              q.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+              q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+              q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+              q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+            } else {
+              q.x = __float_as_uint(v[4 * j + 0]);
+              q.y = __float_as_uint(v[4 * j + 1]);
+              q.z = __float_as_uint(v[4 * j + 2]);
+              q.w = __float_as_uint(v[4 * j + 3]);
+            }
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = q;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < m && col < n) tma_store_2d(&tmap_c, buf, col, row0);
+            else asm volatile("cp.async.bulk.commit_group;" ::: "memory");     // keep the group count in step
+          }
+          ++nstore;
+        } else if (row < m && col < n) {
           OutT* dst = c + (int64_t)row * ldc + col;
-          if (col + 32 <= n && ((ldc * (int)sizeof(OutT)) % 16 == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float t8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) t8[e] = v[j + e];
-              tsp::st8(dst, j, t8);
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < n; ++j) tsp::st(dst, j, v[j]);
-          }
+          for (int j = 0; j < kCols; ++j)       // constant indices only: v stays in registers
+            if (col + j < n) tsp::st(dst, j, v[j]);
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty_bar + acc), 0));
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staging buffers are free again
+    __syncwarp();
   }
   if (*((volatile int*)status) != 0) {
     // a wait ran out somewhere: give TMA loads and MMAs that are still in flight time to land before the pair's
@@ -321,11 +374,27 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_store_map(CUtensorMap* map, void* ptr, int rows, int cols, int ld, bool bf16) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename OutT>
 int launch(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
            int epi, int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (!make_map(&ta, a, m, k, lda, BM) || !make_map(&tb, b, n, k, ldb, BN / 2)) return -6;
+  CUtensorMap tc = ta;          // placeholder when C cannot be described (the kernel then stores directly)
+  const bool aligned_c = (((uintptr_t)c & 15) == 0) && ((ldc * (int)sizeof(OutT)) % 16 == 0);
+  const int tma_store = aligned_c && make_store_map(&tc, c, m, n, ldc, sizeof(OutT) == 2) ? 1 : 0;
   auto kern = gemm_tcgen05_2cta_kernel<OutT>;
   static bool attr_set[64] = {};
   static int n_sm[64] = {};
@@ -354,7 +423,7 @@ int launch(const void* a, const void* b, void* c, const float* bias, int m, int 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, (OutT*)c, bias, m, n, k, ldc, epi, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tma_store, (OutT*)c, bias, m, n, k, ldc, epi, status);
   return (int)e;
 }
 

@@ -6,31 +6,35 @@ import torch.nn.functional as F
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (200, 136, 72), (1024, 768, 768),
-                                   (4096, 4096, 256)])
-def test_matmul_nt_matches_fp32_reference(m, n, k):
+@pytest.mark.parametrize("two_cta", [False, True])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 128), (384, 512, 320), (200, 136, 72), (300, 100, 64),
+                                   (1024, 768, 768), (4096, 4096, 256)])
+def test_matmul_nt_matches_fp32_reference(m, n, k, two_cta):
+    """Both kernels (one CTA per tile; CTA pair per tile with TMA-store epilogue), ragged edges included:
+    (300, 100) has a bf16 row pitch that is no multiple of 16 bytes, which takes the direct-store epilogue."""
     from tspipe_b200.ops import gemm
     torch.manual_seed(0)
     dev = torch.device("cuda", 0)
     a = torch.randn(m, k, device=dev).bfloat16()
     b = torch.randn(n, k, device=dev).bfloat16()
-    c = gemm.matmul_nt(a, b, out_dtype=torch.float32)
+    c = gemm.matmul_nt(a, b, out_dtype=torch.float32, two_cta=two_cta)
     gemm.check_status()
     ref = a.float() @ b.float().t()
     torch.testing.assert_close(c, ref, rtol=1e-3, atol=1e-2 * (k ** 0.5) / 8)
-    c16 = gemm.matmul_nt(a, b)
+    c16 = gemm.matmul_nt(a, b, two_cta=two_cta)
     gemm.check_status()
     torch.testing.assert_close(c16.float(), ref, rtol=2e-2, atol=0.1 * (k ** 0.5) / 8)
 
 
-def test_bias_gelu_epilogue():
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_bias_gelu_epilogue(two_cta):
     from tspipe_b200.ops import gemm
     torch.manual_seed(1)
     dev = torch.device("cuda", 0)
     a = (torch.randn(512, 256, device=dev) * 0.5).bfloat16()
     b = (torch.randn(384, 256, device=dev) * 0.1).bfloat16()
     bias = torch.randn(384, device=dev)
-    y = gemm.matmul_nt(a, b, bias, gelu=True, out_dtype=torch.float32)
+    y = gemm.matmul_nt(a, b, bias, gelu=True, out_dtype=torch.float32, two_cta=two_cta)
     gemm.check_status()
     ref = F.gelu(a.float() @ b.float().t() + bias)
     torch.testing.assert_close(y, ref, rtol=1e-3, atol=1e-3)
