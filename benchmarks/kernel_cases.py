@@ -1,6 +1,7 @@
 """Small stand-alone cases of the hand-written kernels, for profiling one kernel at a time.
 
     python benchmarks/kernel_cases.py bn        # fused BatchNorm fwd/bwd on one ResNet-50 activation
+    python benchmarks/kernel_cases.py bn_r50    # all 53 BatchNorm layers of ResNet-50, forward + backward
     python benchmarks/kernel_cases.py lars      # flat LARS + fused EMA step over 25 M parameters
     python benchmarks/kernel_cases.py ema       # momentum-teacher update over 25 M parameters
     python benchmarks/kernel_cases.py kd        # soft-target KD loss on [2048, 1000] logits
@@ -52,6 +53,55 @@ def case_bn():
     tb = _time(lambda: torch.autograd.grad(y, x, g, retain_graph=True), flush=flush)
     print(f"bn fwd  {shp}: {tf:8.1f} us  {3 * nbytes / tf / 1e6:5.2f} TB/s (read x twice, write y)")
     print(f"bn bwd  {shp}: {tb:8.1f} us  {5 * nbytes / tb / 1e6:5.2f} TB/s (read dy,x twice, write dx)")
+
+
+# BatchNorm inputs of ResNet-50 at 224 x 224 (channels, side, residual?, count): stem, then per stage the three
+# normalisations of each bottleneck (+ the downsample one)
+R50_BN = [(64, 112, False, 1)] + \
+    [(64, 56, False, 6), (256, 56, True, 3), (256, 56, False, 1)] + \
+    [(128, 56, False, 1), (128, 28, False, 7), (512, 28, True, 4), (512, 28, False, 1)] + \
+    [(256, 28, False, 1), (256, 14, False, 11), (1024, 14, True, 6), (1024, 14, False, 1)] + \
+    [(512, 14, False, 1), (512, 7, False, 5), (2048, 7, True, 3), (2048, 7, False, 1)]
+
+
+def case_bn_r50():
+    """Every BatchNorm of one ResNet-50 forward + backward at batch 128 (no L2 flush between layers, as in
+    the model): fused statistics + apply kernels against ATen batch_norm (+ add + relu)."""
+    import torch.nn.functional as F
+    from tspipe_b200.batchnorm import DeferredBatchNorm
+    from tspipe_b200.ops import bn as fbn
+    dev = torch.device("cuda")
+    layers = []
+    total = 0
+    for c, side, res, count in R50_BN:
+        shp = (128, c, side, side)
+        x = torch.randn(shp, device=dev).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+        r = torch.randn_like(x) if res else None
+        bn = DeferredBatchNorm(c, chunks=10 ** 9).to(dev)
+        layers.append((bn, x, r, torch.randn_like(x), count))
+        total += x.numel() * 2 * count
+
+    def ours(backward):
+        for bn, x, r, g, count in layers:
+            for _ in range(count):
+                y = fbn.bn_act(bn, x, r, True)
+                if backward:
+                    torch.autograd.grad(y, x, g)
+
+    def aten(backward):
+        for bn, x, r, g, count in layers:
+            for _ in range(count):
+                y = F.batch_norm(x, None, None, bn.weight.bfloat16(), bn.bias.bfloat16(), True)
+                y = F.relu(y + r if r is not None else y)
+                if backward:
+                    torch.autograd.grad(y, x, g)
+
+    for name, fn in (("fused kernels", ours), ("ATen", aten)):
+        tf = _time(lambda: fn(False), n=3)
+        tfb = _time(lambda: fn(True), n=3)
+        print(f"R50 BatchNorm x53, batch 128, {total / 1e9:.2f} GB of activations, {name:14s}: "
+              f"forward {tf / 1e3:6.2f} ms   forward+backward {tfb / 1e3:6.2f} ms")
+    print("streaming-kernel status:", fbn.stream_status())
 
 
 def case_lars():
@@ -144,5 +194,5 @@ def case_infonce():
 
 
 if __name__ == "__main__":
-    {"bn": case_bn, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
+    {"bn": case_bn, "bn_r50": case_bn_r50, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
      "infonce": case_infonce}[sys.argv[1]]()

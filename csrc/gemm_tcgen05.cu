@@ -4,8 +4,8 @@
 //     shared-memory ring, one elected producer thread;
 //   * tcgen05.mma.cta_group::1.kind::f16 (UMMA 128 x BN x 16) issued by one elected thread, accumulators in
 //     tensor memory (TMEM), smem slots released with tcgen05.commit -> mbarrier;
-//   * four epilogue warps read the accumulator with tcgen05.ld (32 lanes x 32 columns per instruction), fuse
-//     bias / GELU, convert and store 16-byte vectors.
+//   * four epilogue warps read the accumulator with tcgen05.ld, fuse bias / GELU, convert, stage 32-row x 128-byte
+//     blocks in swizzled shared memory and write them with TMA stores (direct stores when C is not 16-byte aligned).
 // Reference call sites: every nn.Linear of the ViT / BERT blocks and heads (library GEMMs there:
 // `benchmarks/moco-v3/vits.py`, `benchmarks/distilbert/bert.py`, `benchmarks/byol/models/mlp_head.py`).
 //
@@ -90,7 +90,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -101,10 +101,26 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// TMA store of one 32-row x 128-byte block (128-byte swizzle) from shared memory; rows / columns beyond the
+// tensor's extent are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+constexpr int kStoreBufBytes = 32 * 128;             // 32 rows x 128 bytes of C = one TMA store
+constexpr int kStoreBytes = 4 * 2 * kStoreBufBytes;  // two staging buffers per epilogue warp
 
 template <int BN>
 struct Cfg {
@@ -112,11 +128,11 @@ struct Cfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN;             // two accumulator buffers; power of two, <= 512
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 // epilogue modes
-constexpr int EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2;
+constexpr int EPI_NONE = 0, EPI_BIAS_GELU = 2;   // 1 = bias only
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -133,12 +149,13 @@ struct BMaps {
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ BMaps bmaps,
-                    int rows_per_b, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc,
+                    const __grid_constant__ CUtensorMap tmap_c, int tma_store, int rows_per_b, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc,
                     int epi, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   using C = Cfg<BN>;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(tiles + kStages * C::kStageBytes);
+  uint8_t* store_bufs = tiles + kStages * C::kStageBytes;   // 1024-aligned: the swizzle follows address bits
+  uint64_t* bars = (uint64_t*)(store_bufs + kStoreBytes);
   uint64_t* full_bar = bars;                         // [kStages]  TMA -> MMA
   uint64_t* empty_bar = bars + kStages;              // [kStages]  MMA -> TMA
   uint64_t* tmem_full_bar = bars + 2 * kStages;      // [2]        MMA -> epilogue
@@ -232,8 +249,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lanes 32*(warp%4) .. +31 ----------------
+    // Blocks of 128 output bytes per row (64 bf16 or 32 fp32 columns) go TMEM -> registers -> (bias, GELU,
+    // convert) -> swizzled shared memory -> one TMA store of 32 rows; two staging buffers per warp, so the
+    // store of block i overlaps the conversion of block i + 1.  Without a usable tensor map for C (unaligned
+    // base or row pitch) every thread stores its own row directly.
+    constexpr int kCols = 128 / (int)sizeof(OutT);
     const int quarter = warp & 3;
-    uint32_t lt = 0;
+    uint8_t* my_bufs = store_bufs + quarter * 2 * kStoreBufBytes;
+    uint32_t lt = 0, nstore = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
@@ -241,38 +264,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       ok = mbar_wait(tmem_full_bar + acc, use & 1, status, 3);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = m0 + quarter * 32 + lane;
+      const int row0 = m0 + quarter * 32, row = row0 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, r);
+      for (int c0 = 0; c0 < BN; c0 += kCols) {
+        float v[kCols];
+        {
+          uint32_t r[kCols];
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0;
+          tmem_ld_32x32_issue(taddr, r);
+          if constexpr (kCols == 64) tmem_ld_32x32_issue(taddr + 32, r + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) v[j] = __uint_as_float(r[j]);
+        }
         const int col = n0 + c0;
-        if (row < m && col < n) {
-          float v[32];
+        if (epi != EPI_NONE && col < n) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (epi != EPI_NONE) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float bj = (col + j < n) ? bias[col + j] : 0.f;
-              v[j] += bj;
-              if (epi == EPI_BIAS_GELU) v[j] = gelu_erf(v[j]);
-            }
+          for (int j = 0; j < kCols; ++j) {
+            v[j] += (col + j < n) ? bias[col + j] : 0.f;
+            if (epi == EPI_BIAS_GELU) v[j] = gelu_erf(v[j]);
           }
+        }
+        if (tma_store) {
+          uint8_t* buf = my_bufs + (nstore & 1) * kStoreBufBytes;
+          if (nstore >= 2) {         // the store issued two blocks ago has finished reading this buffer
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+          }
+          uint8_t* my_row = buf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {   // 16-byte piece j of this row sits at piece (j ^ (row & 7))
+            uint4 q;
+            if constexpr (kCols == 64) {
+              q.x = pack_bf16x2(v[8 * j + 0], v[8 * j + 1]);
+              q.y = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+              q.z = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]);
+              q.w = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+            } else {
+              q.x = __float_as_uint(v[4 * j + 0]);
+              q.y = __float_as_uint(v[4 * j + 1]);
+              q.z = __float_as_uint(v[4 * j + 2]);
+              q.w = __float_as_uint(v[4 * j + 3]);
+            }
+            *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = q;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (row0 < m && col < n) tma_store_2d(&tmap_c, buf, col, row0);
+            else asm volatile("cp.async.bulk.commit_group;" ::: "memory");     // keep the group count in step
+          }
+          ++nstore;
+        } else if (row < m && col < n) {
           OutT* dst = c + (int64_t)row * ldc + col;
-          if (col + 32 <= n && ((ldc * (int)sizeof(OutT)) % 16 == 0)) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float t8[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) t8[e] = v[j + e];
-              tsp::st8(dst, j, t8);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)        // constant indices only: v stays in registers
-              if (col + j < n) tsp::st(dst, j, v[j]);
-          }
+          for (int j = 0; j < kCols; ++j)       // constant indices only: v stays in registers
+            if (col + j < n) tsp::st(dst, j, v[j]);
         }
       }
       // this warp has drained its quarter of the accumulator: hand the buffer back to the MMA issuer
@@ -280,6 +327,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar + acc);
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staging buffers are free again
+    __syncwarp();
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -321,6 +370,19 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_store_map(CUtensorMap* map, void* ptr, int rows, int cols, int ld, bool bf16) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return false;
+  const int esz = bf16 ? 2 : 4;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, typename OutT>
 int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, const float* bias, int m, int n,
            int k, int lda, int ldb, int ldc, int epi, int* status, cudaStream_t stream) {
@@ -332,24 +394,26 @@ int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* 
     const int rows = n_src == 1 ? n : rows_per_b;
     if (!make_map(&tb.m[i], b_srcs[src], rows, k, ldb, BN)) return -6;
   }
+  CUtensorMap tc = ta;          // placeholder when C cannot be described (the kernel then stores directly)
+  const bool aligned_c = (((uintptr_t)c & 15) == 0) && ((ldc * (int)sizeof(OutT)) % 16 == 0);
+  const int tma_store = aligned_c && make_store_map(&tc, c, m, n, ldc, sizeof(OutT) == 2) ? 1 : 0;
   auto kern = gemm_tcgen05_kernel<BN, OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};
+  static int n_sm[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev &= 63;
+  if (!attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-    if (n_sm <= 0) n_sm = 148;
+    cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm[dev] <= 0) n_sm[dev] = 148;
+    attr_set[dev] = true;
   }
   const int num_tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
-  const int grid = num_tiles < n_sm ? num_tiles : n_sm;
-  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, n_src == 1 ? n + BN : rows_per_b, (OutT*)c, bias, m, n,
-                                                        k, ldc, epi, status);
+  const int grid = num_tiles < n_sm[dev] ? num_tiles : n_sm[dev];
+  kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, tc, tma_store, n_src == 1 ? n + BN : rows_per_b,
+                                                        (OutT*)c, bias, m, n, k, ldc, epi, status);
   return TSP_LAUNCH_CHECK();
 }
 

@@ -47,6 +47,7 @@ int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int
 
 // ---- batchnorm.cu -----------------------------------------------------------------------------------------------
 int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
+int tsp_bn_stream_status(int reset);
 int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
                  const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq,
                  float* acc_count, int64_t m, int c, float eps, int relu, int dtype, cudaStream_t stream);

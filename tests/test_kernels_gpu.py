@@ -192,7 +192,11 @@ def test_gelu_bias(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape,residual,relu", [((8, 64, 14, 14), True, True), ((4, 256, 7, 7), False, True),
                                                 ((16, 24, 5, 3), False, False), ((32, 512), False, True),
-                                                ((3, 2048, 2, 2), True, True)])
+                                                ((3, 2048, 2, 2), True, True),
+                                                # >= 1 MB in bf16: the bulk-copy streaming statistics kernels
+                                                ((64, 64, 28, 28), True, True), ((32, 256, 14, 14), False, True),
+                                                ((16, 2048, 7, 7), True, True), ((48, 128, 9, 11), False, True),
+                                                ((64, 64, 16, 16), False, False)])
 def test_fused_batchnorm_act(dtype, shape, residual, relu):
     """Fused BN(+residual)(+ReLU) forward and backward vs. fp32 F.batch_norm + add + relu; the deferred
     accumulators must receive the microbatch sums."""
@@ -233,6 +237,7 @@ def test_fused_batchnorm_act(dtype, shape, residual, relu):
     torch.testing.assert_close(bn.sum, xf.sum(dims), rtol=1e-3, atol=1e-2)
     torch.testing.assert_close(bn.sum_squares, (xf * xf).sum(dims), rtol=1e-3, atol=1e-2)
     assert bn.tracked == 1 and bn.counter == x.numel() // c
+    assert fbn.stream_status() == 0
 
 
 def test_fused_batchnorm_eval_uses_running_stats():

@@ -59,6 +59,14 @@ def _lib():
     return L
 
 
+def stream_status(reset: bool = False) -> int:
+    """0 unless a bounded wait of the streaming statistics kernels ran out on the current device
+    (1 = producer, 2 = consumer).  Synchronises the device."""
+    L = _lib()
+    L.tsp_bn_stream_status.restype = _c.c_int
+    return int(L.tsp_bn_stream_status(_c.c_int(1 if reset else 0)))
+
+
 class _BnAct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None):
