@@ -2,6 +2,7 @@
 
     python benchmarks/kernel_cases.py bn        # fused BatchNorm fwd/bwd on one ResNet-50 activation
     python benchmarks/kernel_cases.py bn_r50    # all 53 BatchNorm layers of ResNet-50, forward + backward
+    python benchmarks/kernel_cases.py stem      # tcgen05 stem convolution 7x7/2 on [128, 3, 224, 224]
     python benchmarks/kernel_cases.py lars      # flat LARS + fused EMA step over 25 M parameters
     python benchmarks/kernel_cases.py ema       # momentum-teacher update over 25 M parameters
     python benchmarks/kernel_cases.py kd        # soft-target KD loss on [2048, 1000] logits
@@ -104,6 +105,26 @@ def case_bn_r50():
     print("streaming-kernel status:", fbn.stream_status())
 
 
+def case_stem():
+    """ResNet stem convolution [128, 3, 224, 224] -> [128, 64, 112, 112] (+ BatchNorm statistics) against the
+    library convolution followed by the statistics kernel."""
+    import torch.nn.functional as F
+    from tspipe_b200.ops import conv, gemm
+    dev = torch.device("cuda")
+    x = torch.randn(128, 3, 224, 224, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    w = torch.randn(64, 3, 7, 7, device=dev) * 0.05
+    wb = w.bfloat16().contiguous(memory_format=torch.channels_last)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    torch.backends.cudnn.benchmark = True
+    t = _time(lambda: conv.stem_conv(x, w), n=10, flush=flush)
+    tr = _time(lambda: F.conv2d(x, wb, stride=2, padding=3), n=10, flush=flush)
+    gemm.check_status()
+    out_bytes = 128 * 64 * 112 * 112 * 2
+    flops = 2 * 128 * 112 * 112 * 64 * 147
+    print(f"stem conv 7x7/2 [128,3,224,224]: {t:8.1f} us  ({(out_bytes + x.numel() * 2) / t / 1e6:5.2f} TB/s, "
+          f"{flops / t / 1e6:6.1f} TFLOP/s)   library: {tr:8.1f} us")
+
+
 def case_lars():
     from tspipe_b200.optim import LARS
     from tspipe_b200.runtime.state import FlatParams
@@ -194,5 +215,5 @@ def case_infonce():
 
 
 if __name__ == "__main__":
-    {"bn": case_bn, "bn_r50": case_bn_r50, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
+    {"bn": case_bn, "bn_r50": case_bn_r50, "stem": case_stem, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
      "infonce": case_infonce}[sys.argv[1]]()

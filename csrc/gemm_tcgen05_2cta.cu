@@ -264,7 +264,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
       const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM, n0 = (t / tiles_m) * BN;
       const uint32_t acc = lt & 1, use = lt >> 1;
-      ok = mbar_wait(tmem_full_bar + acc, use & 1, status, 3);
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3));   // one way out per warp
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row0 = m0 + quarter * 32, row = row0 + lane;

@@ -82,6 +82,10 @@ int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, i
 int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, int m, int k,
                                 int lda, int ldb, int ldc, int out_dtype, int* status, cudaStream_t stream);
 
+// ---- conv_stem_tcgen05.cu -----------------------------------------------------------------------------------------
+int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int* status,
+                      cudaStream_t stream);
+
 // ---- gemm_tcgen05_2cta.cu -----------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn_2cta(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda,
                           int ldb, int ldc, int out_dtype, int epi, int* status, cudaStream_t stream);

@@ -69,7 +69,7 @@ def stream_status(reset: bool = False) -> int:
 
 class _BnAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None):
+    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None, pre_sums=None):
         m, c = _as_rows(x)
         dt = _f._dt(x)
         L = _lib()
@@ -78,13 +78,14 @@ class _BnAct(torch.autograd.Function):
             if residual.dtype != x.dtype or _as_rows(residual) != (m, c):
                 residual = residual.to(x.dtype).contiguous(
                     memory_format=torch.channels_last if x.dim() == 4 else torch.contiguous_format)
-        sums = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+        # statistics handed over by the producer of x (a convolution epilogue) replace the statistics pass
+        sums = pre_sums if pre_sums is not None else torch.empty(2 * c, dtype=torch.float32, device=x.device)
         save = torch.empty(2 * c, dtype=torch.float32, device=x.device)
         wf = weight.detach() if weight.dtype == torch.float32 else weight.detach().float()
         bf = bias.detach() if bias.dtype == torch.float32 else bias.detach().float()
         with torch.cuda.device(x.device):
             st = _f._stream()
-            if fixed is None:
+            if fixed is None and pre_sums is None:
                 _f._check(L.tsp_bn_stats(_f._ptr(x), _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums), st),
                           "tsp_bn_stats")
                 _f._count(2)
@@ -134,13 +135,15 @@ class _BnAct(torch.autograd.Function):
             gres = dres if dres is not None else dy
         else:
             gres = None
-        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None, None
+        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None, None, None
 
 
-def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = False) -> torch.Tensor:
+def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = False,
+           sums: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``relu(bn(x) + residual)`` with the statistics semantics of ``bn`` (plain running-stat
     BatchNorm, or :class:`~tspipe_b200.batchnorm.DeferredBatchNorm` whose accumulators are fed by the
-    same statistics pass)."""
+    same statistics pass).  ``sums`` = per-channel [sum | sum of squares] of ``x`` when its producer already
+    computed them (used in training mode only)."""
     if not applicable(bn, x):
         y = bn(x)
         if residual is not None:
@@ -154,16 +157,17 @@ def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: b
         return y
     if isinstance(bn, DeferredBatchNorm) and bn.group is not None:
         # the partition's statistics live in flat buffers; the group commits them (one launch set per mini-batch)
-        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, bn.count)
+        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, bn.count,
+                            sums)
         return y
     if isinstance(bn, DeferredBatchNorm):
-        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares)
+        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, None, sums)
         bn.counter += m
         bn.tracked += 1
         if bn.tracked == bn.chunks:
             bn._commit()
         return y
-    y, sums = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, None, None)
+    y, sums = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, None, None, None, sums)
     if bn.track_running_stats and bn.running_mean is not None:
         with torch.no_grad():
             bn.num_batches_tracked += 1

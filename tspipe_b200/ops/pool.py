@@ -15,7 +15,7 @@ class _MaxPool(torch.autograd.Function):
     def forward(ctx, x):
         n, c, h, w = x.shape
         ho, wo = (h + 1) // 2, (w + 1) // 2
-        y = torch.empty((n, c, ho, wo), dtype=x.dtype, device=x.device).contiguous(memory_format=torch.channels_last)
+        y = torch.empty((n, c, ho, wo), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
         need_idx = x.requires_grad
         idx = torch.empty((n, ho, wo, c), dtype=torch.uint8, device=x.device) if need_idx else None
         L = _f.lib()
@@ -34,7 +34,7 @@ class _MaxPool(torch.autograd.Function):
         (idx,) = ctx.saved_tensors
         n, c, h, w = ctx.shape
         dy = dy.contiguous(memory_format=torch.channels_last)
-        dx = torch.empty((n, c, h, w), dtype=dy.dtype, device=dy.device).contiguous(memory_format=torch.channels_last)
+        dx = torch.empty((n, c, h, w), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
         L = _f.lib()
         L.tsp_maxpool3x3s2_bwd.restype = _c.c_int
         with torch.cuda.device(dy.device):

@@ -239,6 +239,9 @@ class StageEngine:
         if self.channels_last:
             self.online.to(memory_format=torch.channels_last)
             self.target.to(memory_format=torch.channels_last)
+        if self.fused:
+            from .fuse import fuse_partition
+            self.online, self.target = fuse_partition(self.online), fuse_partition(self.target)
         self.online.train()
         self.target.train(target_train_mode)
         for p in self.target.parameters():
@@ -548,10 +551,38 @@ class StageEngine:
         ub = cache[v][op.ub]
         data = ub.value if isinstance(ub, Batch) else ub
         if self.cuda:
-            if msg.ready_event is not None:
-                torch.cuda.current_stream().wait_event(msg.ready_event)
-            data = pt.tree_map_tensors(lambda t: t if t.is_cuda else self._h2d(t), data)
+            # Online and target network read the same views: copy to the device and convert (bf16, channels-last,
+            # one kernel) once per view and microbatch, on the compute stream that both forwards run on.
+            prepared = getattr(msg, "_prepared", None)
+            if prepared is None:
+                prepared = {}
+                msg._prepared = prepared
+            pkey = (v, op.ub)
+            if pkey not in prepared:
+                if msg.ready_event is not None:
+                    torch.cuda.current_stream().wait_event(msg.ready_event)
+                data = pt.tree_map_tensors(lambda t: t if t.is_cuda else self._h2d(t), data)
+                if self._conv_input():
+                    data = pt.tree_map_tensors(_to_conv_input, data)
+                prepared[pkey] = data
+            data = prepared[pkey]
         return data
+
+    def _conv_input(self) -> bool:
+        """True when both networks start with a convolution under bf16 autocast: the cast that autocast would
+        do per network and the channels-last conversion can then be one shared kernel per view."""
+        flag = getattr(self, "_conv_input_flag", None)
+        if flag is None:
+            def first_leaf(m):
+                while True:
+                    ch = list(m.children())
+                    if not ch:
+                        return m
+                    m = ch[0]
+            flag = bool(self.autocast and self.channels_last and
+                        all(isinstance(first_leaf(m), nn.Conv2d) for m in (self.online, self.target)))
+            self._conv_input_flag = flag
+        return flag
 
     def _h2d(self, t: torch.Tensor) -> torch.Tensor:
         cur = torch.cuda.current_stream()
@@ -892,6 +923,12 @@ class StageEngine:
                 link.flush()
         if self.cuda:
             self.compute.synchronize()
+
+
+def _to_conv_input(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() == 4 and t.dtype == torch.float32:
+        return t.to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    return t
 
 
 def _to_channels_last(t: torch.Tensor) -> torch.Tensor:
