@@ -217,7 +217,7 @@ def measure(a, pp, dp, ub, split, e2e):
         prof.device_events.clear()
     out = {"value": round(global_batch * a.steps / (ms / 1e3), 2), "ms_per_step": round(ms / a.steps, 3),
            "gpu_launches": launches, "clocks": clocks, "parallelism": f"dp{dp}xpp{pp}", "microbatches": ub,
-           "bwd_split": split, "global_batch": global_batch, "last_loss": round(losses[-1], 5) if losses else None}
+           "bwd_split": split, "global_batch": global_batch, "merged_views": bool(tsp.engine.merge_views), "last_loss": round(losses[-1], 5) if losses else None}
     if e2e:
         for i in range(min(a.warmup, 3)):
             feed(i, True)
@@ -267,6 +267,8 @@ def run_ours(a):
            "config": {"model": f"byol_{a.model}+mlp4096-256", "global_batch": r["global_batch"], "seq_len": None,
                       "image": a.image, "parallelism": r["parallelism"], "microbatches": r["microbatches"],
                       "bwd_split": r["bwd_split"], "optimizer": "LARS", "ema": 0.996,
+                      "views": "both views of a network in one stacked forward, BatchNorm statistics per view"
+                               if r.get("merged_views") else "one forward per view",
                       "l2_policy": "inputs larger than L2 (154 MB per replica step)",
                       "timing": "CUDA events on the compute stream around K feeds + flush, max over ranks"}}
     if r.get("last_loss") is not None:

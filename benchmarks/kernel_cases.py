@@ -186,9 +186,14 @@ def case_gemm():
     m, n, k = 8192, 3072, 768
     a = torch.randn(m, k, device=dev).bfloat16()
     b = torch.randn(n, k, device=dev).bfloat16()
-    t = _time(lambda: gemm.matmul_nt(a, b), n=10)
-    tr = _time(lambda: a @ b.t(), n=10)
-    print(f"tcgen05 gemm {m}x{n}x{k}: {t:8.1f} us  {2 * m * n * k / t / 1e6:7.1f} TFLOP/s   (library: {tr:8.1f} us)")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    t2 = _time(lambda: gemm.matmul_nt(a, b, two_cta=True), n=10, flush=flush)
+    t1 = _time(lambda: gemm.matmul_nt(a, b, two_cta=False), n=10, flush=flush)
+    tr = _time(lambda: a @ b.t(), n=10, flush=flush)
+    gemm.check_status()
+    f = 2 * m * n * k / 1e6
+    print(f"tcgen05 gemm {m}x{n}x{k}: CTA pair {t2:7.1f} us {f / t2:7.1f} TFLOP/s | one CTA {t1:7.1f} us {f / t1:7.1f} TFLOP/s"
+          f" | library {tr:7.1f} us {f / tr:7.1f} TFLOP/s")
 
 
 def case_infonce():

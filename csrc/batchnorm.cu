@@ -44,6 +44,15 @@ __global__ void __launch_bounds__(kBlock, MODE == 0 ? 5 : 2) bn_colsum_kernel(co
                                                            const float* __restrict__ w, const float* __restrict__ bias,
                                                            int relu, int64_t m, int c, float* __restrict__ out) {
   extern __shared__ float sm[];
+  {   // blockIdx.z = segment: an independent group of m rows with its own statistics
+    const int64_t so = (int64_t)blockIdx.z * m * c;
+    x += so;
+    if (dy != nullptr) dy += so;
+    if (y != nullptr) y += so;
+    if (dres != nullptr) dres += so;
+    if (mean_rstd != nullptr) mean_rstd += (int64_t)blockIdx.z * 2 * c;
+    out += (int64_t)blockIdx.z * 2 * c;
+  }
   const int cpv = c >> 3;
   const Tile tl = make_tile(cpv);
   const int tx = threadIdx.x % tl.tx_n, ty = threadIdx.x / tl.tx_n;
@@ -204,6 +213,15 @@ bn_colsum_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         const float* __restrict__ bias, int relu, int64_t m, int c, int chunk,
                         float* __restrict__ out) {
   extern __shared__ __align__(128) uint8_t stream_smem[];
+  {   // blockIdx.y = segment: an independent group of m rows with its own statistics
+    const int64_t so = (int64_t)blockIdx.y * m * c;
+    x += so;
+    if (dy != nullptr) dy += so;
+    if (y != nullptr) y += so;
+    if (dres != nullptr) dres += so;
+    if (mean_rstd != nullptr) mean_rstd += (int64_t)blockIdx.y * 2 * c;
+    out += (int64_t)blockIdx.y * 2 * c;
+  }
   const int narr = MODE == 0 ? 1 : (y != nullptr ? 3 : 2);
   const int stage_bytes = narr * chunk;
   uint8_t* bufs = stream_smem;
@@ -364,9 +382,19 @@ __global__ void __launch_bounds__(kBlock) bn_apply_kernel(const T* __restrict__ 
                                                           const float* __restrict__ w, const float* __restrict__ b,
                                                           float* __restrict__ save_mean_rstd,
                                                           float* __restrict__ acc_sum, float* __restrict__ acc_sumsq,
-                                                          float* __restrict__ acc_count, int64_t m, int c, float eps,
-                                                          int relu) {
+                                                          float* __restrict__ acc_count, int64_t acc_seg_stride,
+                                                          int64_t m, int c, float eps, int relu) {
   extern __shared__ float sm[];
+  {   // blockIdx.y = segment: m rows with their own statistics (and their own set of accumulators)
+    const int64_t so = (int64_t)blockIdx.y * m * c;
+    x += so;
+    y += so;
+    if (res != nullptr) res += so;
+    if (sums != nullptr) sums += (int64_t)blockIdx.y * 2 * c;
+    if (save_mean_rstd != nullptr) save_mean_rstd += (int64_t)blockIdx.y * 2 * c;
+    if (acc_sum != nullptr) { acc_sum += blockIdx.y * acc_seg_stride; acc_sumsq += blockIdx.y * acc_seg_stride; }
+    if (acc_count != nullptr) acc_count += blockIdx.y * acc_seg_stride;
+  }
   float* scale = sm;
   float* shift = sm + c;
   const float inv_m = 1.f / (float)m;
@@ -470,6 +498,15 @@ __global__ void __launch_bounds__(kBlock) bn_bwd_apply_kernel(const T* __restric
                                                               const float* __restrict__ sums, T* __restrict__ dx,
                                                               int64_t m, int c) {
   extern __shared__ float sm[];
+  {   // blockIdx.y = segment
+    const int64_t so = (int64_t)blockIdx.y * m * c;
+    dy += so;
+    x += so;
+    dx += so;
+    if (y != nullptr) y += so;
+    mean_rstd += (int64_t)blockIdx.y * 2 * c;
+    sums += (int64_t)blockIdx.y * 2 * c;
+  }
   float* s_a = sm;
   float* s_b = sm + c;
   float* s_d = sm + 2 * c;
@@ -582,7 +619,7 @@ inline bool stream_ok(int64_t m, int c, int dtype) {
 
 template <int MODE>
 int launch_stream(const void* x, const void* dy, const void* y, void* dres, const float* mean_rstd, const float* w,
-                  const float* bias, int relu, int64_t m, int c, float* sums, cudaStream_t stream) {
+                  const float* bias, int relu, int64_t m, int c, int segs, float* sums, cudaStream_t stream) {
   const int narr = MODE == 0 ? 1 : (y != nullptr ? 3 : 2);
   const int64_t row_bytes = (int64_t)c * 2;
   // bytes per array and stage: 32 KB for one streamed array, 16 KB for two or three (at most 192 KB of ring);
@@ -591,7 +628,8 @@ int launch_stream(const void* x, const void* dy, const void* y, void* dres, cons
   while (chunk > 8192 && m * row_bytes < (int64_t)148 * 4 * chunk) chunk >>= 1;
   if (chunk < row_bytes) chunk = (int)row_bytes;
   const int64_t rows_per_chunk = chunk / row_bytes;
-  int64_t grid = 148;
+  int64_t grid = 148 / segs;                     // CTAs per segment: one CTA per SM over all segments
+  if (grid < 1) grid = 1;
   const int64_t want = (m + 2 * rows_per_chunk - 1) / (2 * rows_per_chunk);
   if (want < grid) grid = want < 1 ? 1 : want;
   const size_t smem = (size_t)kStreamStages * narr * chunk + 2 * kStreamStages * 8 + kStreamConsumers * 16 * 4;
@@ -605,7 +643,7 @@ int launch_stream(const void* x, const void* dy, const void* y, void* dres, cons
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  kern<<<(int)grid, kStreamThreads, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
+  kern<<<dim3((unsigned)grid, (unsigned)segs), kStreamThreads, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
                                                     (const __nv_bfloat16*)y, (__nv_bfloat16*)dres, mean_rstd, w, bias,
                                                     relu, m, c, chunk, sums);
   return TSP_LAUNCH_CHECK();
@@ -628,17 +666,21 @@ int tsp_bn_stream_status(int reset) {
 }
 
 // sums [2*c] fp32 is zeroed here, then receives per-channel sum(x) and sum(x^2).
-int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream) {
+// All four entry points take the activation as `segs` consecutive groups of m / segs rows; every group is
+// normalised with its own statistics (two augmented views stacked along the batch axis).  Per-group arrays are
+// laid out group-major: sums [segs][2c], save_mean_rstd [segs][2c].
+int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, int segs, cudaStream_t stream) {
   if (m <= 0) return 0;
-  if (c % 8 != 0 || c > 8192) return -3;
-  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c, stream);
+  if (c % 8 != 0 || c > 8192 || segs < 1 || m % segs != 0) return -3;
+  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c * segs, stream);
   if (e != cudaSuccess) return (int)e;
+  m /= segs;
   if (stream_ok(m, c, dtype))
-    return launch_stream<0>(x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, m, c, sums, stream);
+    return launch_stream<0>(x, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, m, c, segs, sums, stream);
   const int cpv = c / 8;
   const Tile tl = make_tile(cpv);
   const int slabs = (cpv + tl.tx_n - 1) / tl.tx_n;
-  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs);
+  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs, segs);
   const size_t smem = sizeof(float) * 16 * (size_t)tl.tx_n * tl.ty_n;
   if (dtype == TSP_DTYPE_BF16)
     bn_colsum_kernel<__nv_bfloat16, 0><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, nullptr, nullptr, nullptr,
@@ -649,38 +691,47 @@ int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaSt
   return TSP_LAUNCH_CHECK();
 }
 
+// acc_sum / acc_sumsq / acc_count (optional): accumulators of the deferred running statistics; group g adds into
+// acc + g * acc_seg_stride, so that each group's mini-batch can be committed on its own.
 int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
                  const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq,
-                 float* acc_count, int64_t m, int c, float eps, int relu, int dtype, cudaStream_t stream) {
+                 float* acc_count, int64_t acc_seg_stride, int64_t m, int c, float eps, int relu, int dtype, int segs,
+                 cudaStream_t stream) {
   if (m <= 0) return 0;
-  if (c % 8 != 0 || c > 4096) return -3;
+  if (c % 8 != 0 || c > 4096 || segs < 1 || m % segs != 0) return -3;
+  m /= segs;
   const size_t smem = sizeof(float) * 2 * (size_t)c;
-  const int grid = elem_blocks(m * (c / 8));
+  int gx = elem_blocks(m * (c / 8));
+  if (segs > 1 && gx > (148 * 16) / segs) gx = (148 * 16) / segs;
+  const dim3 grid(gx, segs);
   if (dtype == TSP_DTYPE_BF16)
     bn_apply_kernel<__nv_bfloat16><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res,
                                                                    (__nv_bfloat16*)y, sums, fixed_mean_var, w, b,
-                                                                   save_mean_rstd, acc_sum, acc_sumsq, acc_count, m, c, eps,
-                                                                   relu);
+                                                                   save_mean_rstd, acc_sum, acc_sumsq, acc_count,
+                                                                   acc_seg_stride, m, c, eps, relu);
   else
     bn_apply_kernel<float><<<grid, kBlock, smem, stream>>>((const float*)x, (const float*)res, (float*)y, sums,
                                                            fixed_mean_var, w, b, save_mean_rstd, acc_sum, acc_sumsq,
-                                                           acc_count, m, c, eps, relu);
+                                                           acc_count, acc_seg_stride, m, c, eps, relu);
   return TSP_LAUNCH_CHECK();
 }
 
-// sums [2*c] is zeroed, then receives sum(dy') and sum(dy' * xhat) (= db and dw).  `y` non-null applies the ReLU
-// mask; `dres` non-null receives dy'.
+// sums [segs][2*c] is zeroed, then receives per group sum(dy') and sum(dy' * xhat) (db and dw are their sums over
+// the groups).  `y` non-null applies the ReLU mask; `dres` non-null receives dy'.
 int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, const float* mean_rstd, const float* w,
-                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, cudaStream_t stream) {
+                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, int segs,
+                      cudaStream_t stream) {
   if (m <= 0) return 0;
-  if (c % 8 != 0 || c > 8192) return -3;
-  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c, stream);
+  if (c % 8 != 0 || c > 8192 || segs < 1 || m % segs != 0) return -3;
+  cudaError_t e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)c * segs, stream);
   if (e != cudaSuccess) return (int)e;
-  if (stream_ok(m, c, dtype)) return launch_stream<1>(x, dy, y, dres, mean_rstd, w, bias, relu, m, c, sums, stream);
+  m /= segs;
+  if (stream_ok(m, c, dtype))
+    return launch_stream<1>(x, dy, y, dres, mean_rstd, w, bias, relu, m, c, segs, sums, stream);
   const int cpv = c / 8;
   const Tile tl = make_tile(cpv);
   const int slabs = (cpv + tl.tx_n - 1) / tl.tx_n;
-  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs);
+  dim3 grid(row_blocks(m, tl.ty_n, slabs), slabs, segs);
   const size_t smem = sizeof(float) * 16 * (size_t)tl.tx_n * tl.ty_n;
   if (dtype == TSP_DTYPE_BF16)
     bn_colsum_kernel<__nv_bfloat16, 1><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
@@ -693,16 +744,19 @@ int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, 
 }
 
 int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean_rstd, const float* w,
-                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype,
+                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype, int segs,
                      cudaStream_t stream) {
   if (m <= 0) return 0;
-  if (c % 8 != 0 || c > 4096) return -3;
+  if (c % 8 != 0 || c > 4096 || segs < 1 || m % segs != 0) return -3;
+  m /= segs;
   const size_t smem = sizeof(float) * 5 * (size_t)c;
   if (smem > 48 * 1024) {      // opt in to more than the default dynamic shared memory
     cudaFuncSetAttribute(bn_bwd_apply_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     cudaFuncSetAttribute(bn_bwd_apply_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
   }
-  const int grid = elem_blocks(m * (c / 8));
+  int gx = elem_blocks(m * (c / 8));
+  if (segs > 1 && gx > (148 * 16) / segs) gx = (148 * 16) / segs;
+  const dim3 grid(gx, segs);
   if (dtype == TSP_DTYPE_BF16)
     bn_bwd_apply_kernel<__nv_bfloat16><<<grid, kBlock, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                        (const __nv_bfloat16*)y, mean_rstd, w, bias, relu,

@@ -160,7 +160,7 @@ __device__ __forceinline__ void ring_load(uint8_t* ring, const __nv_bfloat16* x,
 
 __global__ void __launch_bounds__(kThreads, 1)
 conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_y,
-                 const __nv_bfloat16* __restrict__ x, int n_img, int h, int w, int oh_n, int ow_n,
+                 const __nv_bfloat16* __restrict__ x, int n_img, int h, int w, int oh_n, int ow_n, int imgs_per_seg,
                  float* __restrict__ sums, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* a_tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -287,9 +287,22 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     const int quarter = warp & 3;
     uint8_t* my_bufs = store_bufs + quarter * 2 * kStoreBufBytes;
     float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;          // channels 2*lane, 2*lane+1
+    int cur_seg = t_begin < t_end ? (t_begin / oh_n) / imgs_per_seg : 0;
+    auto flush_sums = [&](int seg) {
+      if (sums != nullptr) {
+        float* dst = sums + seg * 2 * kCout;
+        atomicAdd(dst + 2 * lane, s0);
+        atomicAdd(dst + 2 * lane + 1, s1);
+        atomicAdd(dst + kCout + 2 * lane, q0);
+        atomicAdd(dst + kCout + 2 * lane + 1, q1);
+      }
+      s0 = s1 = q0 = q1 = 0.f;
+    };
     uint32_t it = 0;
     bool ok = true;
     for (int t = t_begin; t < t_end && ok; ++t, ++it) {
+      const int seg = (t / oh_n) / imgs_per_seg;           // statistics are kept per group of images
+      if (seg != cur_seg) { flush_sums(cur_seg); cur_seg = seg; }
       const uint32_t acc = it & 1, use = it >> 1;
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3));   // one way out per warp
       if (!ok) break;
@@ -326,20 +339,16 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       }
       // statistics of the rounded outputs: lane owns channels 2*lane, 2*lane+1 of the warp's valid rows
       const int valid = ow_n - row0 < 32 ? ow_n - row0 : 32;
-      for (int rr = 0; rr < valid; ++rr) {
+#pragma unroll 8
+      for (int rr = 0; rr < 32; ++rr) {              // fixed trip count: the loads of a group are issued together
         const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) + (lane & 3) * 4);
         const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
-        s0 += f.x; q0 += f.x * f.x; s1 += f.y; q1 += f.y * f.y;
+        if (rr < valid) { s0 += f.x; q0 += f.x * f.x; s1 += f.y; q1 += f.y * f.y; }
       }
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     __syncwarp();
-    if (sums != nullptr) {
-      atomicAdd(sums + 2 * lane, s0);
-      atomicAdd(sums + 2 * lane + 1, s1);
-      atomicAdd(sums + kCout + 2 * lane, q0);
-      atomicAdd(sums + kCout + 2 * lane + 1, q1);
-    }
+    flush_sums(cur_seg);
   }
   if (*((volatile int*)status) != 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);        // let copies and MMAs that are still in flight land
@@ -373,11 +382,13 @@ extern "C" {
 
 // y[n, oh, ow, 64] = conv7x7/2 pad 3 of x[n, h, w, 3] (both bf16, channels-last memory) with wmat[64][192] bf16:
 // wmat[oc][kh*21 + kw*3 + c] = weight[oc][c][kh][kw], zero beyond k = 146.  h even, w % 8 == 0, 8 <= w <= 224.
-// `sums` (optional, 128 floats, zeroed by the caller) receives per-channel sum and sum of squares of y.
+// `sums` (optional, [segs][128] floats, zeroed by the caller) receives per-channel sum and sum of squares of y for
+// each of the `segs` consecutive groups of n / segs images.
 // `status`: one zeroed int in device memory; non-zero afterwards = a bounded wait ran out and y is not valid.
-int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int* status,
-                      cudaStream_t stream) {
+int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int segs,
+                      int* status, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (segs < 1 || n % segs != 0) return -3;
   if ((h & 1) || (w & 7) || w > 224 || h < 8 || w < 8) return -3;
   if ((((uintptr_t)x | (uintptr_t)wmat | (uintptr_t)y) & 15) != 0) return -2;
   const int oh = h / 2, ow = w / 2;
@@ -418,7 +429,7 @@ int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int
   }
   const int tiles = n * oh;
   const int grid = tiles < n_sm[dev] ? tiles : n_sm[dev];
-  conv_stem_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tw, ty, (const __nv_bfloat16*)x, n, h, w, oh, ow, sums, status);
+  conv_stem_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tw, ty, (const __nv_bfloat16*)x, n, h, w, oh, ow, n / segs, sums, status);
   return TSP_LAUNCH_CHECK();
 }
 

@@ -46,15 +46,17 @@ int tsp_gelu_bwd(const void* dy, const void* x, const float* bias, void* dx, int
                  cudaStream_t stream);
 
 // ---- batchnorm.cu -----------------------------------------------------------------------------------------------
-int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
+int tsp_bn_stats(const void* x, int64_t m, int c, int dtype, float* sums, int segs, cudaStream_t stream);
 int tsp_bn_stream_status(int reset);
 int tsp_bn_apply(const void* x, const void* res, void* y, const float* sums, const float* fixed_mean_var,
                  const float* w, const float* b, float* save_mean_rstd, float* acc_sum, float* acc_sumsq,
-                 float* acc_count, int64_t m, int c, float eps, int relu, int dtype, cudaStream_t stream);
+                 float* acc_count, int64_t acc_seg_stride, int64_t m, int c, float eps, int relu, int dtype, int segs,
+                 cudaStream_t stream);
 int tsp_bn_bwd_reduce(const void* dy, const void* x, const void* y, void* dres, const float* mean_rstd, const float* w,
-                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, cudaStream_t stream);
+                      const float* bias, int relu, int64_t m, int c, int dtype, float* sums, int segs,
+                      cudaStream_t stream);
 int tsp_bn_bwd_apply(const void* dy, const void* x, const void* y, const float* mean_rstd, const float* w,
-                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype,
+                     const float* bias, int relu, const float* sums, void* dx, int64_t m, int c, int dtype, int segs,
                      cudaStream_t stream);
 
 // ---- peer.cu ------------------------------------------------------------------------------------------------------
@@ -83,8 +85,8 @@ int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, i
                                 int lda, int ldb, int ldc, int out_dtype, int* status, cudaStream_t stream);
 
 // ---- conv_stem_tcgen05.cu -----------------------------------------------------------------------------------------
-int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int* status,
-                      cudaStream_t stream);
+int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int segs,
+                      int* status, cudaStream_t stream);
 
 // ---- gemm_tcgen05_2cta.cu -----------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn_2cta(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda,

@@ -63,3 +63,19 @@ def test_fused_partition_matches_plain_sequential():
         torch.testing.assert_close(q.grad, p.grad, rtol=5e-2, atol=5e-2 * max(p.grad.abs().max().item(), 1e-3), msg=k)
     torch.testing.assert_close(fused[1].sum, plain[1].sum, rtol=1e-2, atol=1.0)
     torch.testing.assert_close(fused[1].sum_squares, plain[1].sum_squares, rtol=1e-2, atol=1.0)
+
+
+def test_stem_conv_statistics_per_group_of_images():
+    from tspipe_b200.ops import conv, gemm
+    torch.manual_seed(2)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(6, 3, 32, 32, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    x[3:] *= 3.0
+    weight = torch.randn(64, 3, 7, 7, device=dev) * 0.1
+    y, sums = conv.stem_conv(x, weight, segments=2)
+    gemm.check_status()
+    yf = y.float()
+    sums = sums.view(2, 128)
+    for g, part in enumerate((yf[:3], yf[3:])):
+        torch.testing.assert_close(sums[g, :64], part.sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
+        torch.testing.assert_close(sums[g, 64:], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=1e-2)

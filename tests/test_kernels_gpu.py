@@ -359,3 +359,50 @@ def test_maxpool_channels_last(dtype, shape):
     yr.backward(g.float())
     torch.testing.assert_close(y.float(), yr.detach(), rtol=0, atol=0)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("shape,residual", [((8, 64, 14, 14), True), ((64, 64, 28, 28), False), ((32, 256, 14, 14), True),
+                                            ((16, 512), False)])
+def test_batchnorm_stacked_views_match_separate_forwards(shape, residual):
+    """Two views stacked along the batch axis under ``segments(2)`` = two separate fused forwards/backwards:
+    per-view statistics, the same gradients, the same deferred running statistics."""
+    import copy
+    from tspipe_b200.batchnorm import BatchNormGroup, DeferredBatchNorm
+    from tspipe_b200.ops import bn as fbn
+    torch.manual_seed(11)
+    c = shape[1]
+    fmt = torch.channels_last if len(shape) == 4 else torch.contiguous_format
+    mk = lambda s=1.0, o=0.0: (torch.randn(shape, device=_dev()) * s + o).bfloat16().contiguous(memory_format=fmt)
+    xa, xb = mk(1.5, 0.3).requires_grad_(), mk(0.7, -1.0).requires_grad_()
+    ra, rb = (mk().requires_grad_(), mk().requires_grad_()) if residual else (None, None)
+    ga, gb = mk(), mk()
+    net1 = torch.nn.Sequential(DeferredBatchNorm(c, chunks=1)).to(_dev())
+    with torch.no_grad():
+        net1[0].weight.uniform_(0.5, 1.5)
+        net1[0].bias.uniform_(-0.5, 0.5)
+    net2 = copy.deepcopy(net1)
+    g1, g2 = BatchNormGroup(net1), BatchNormGroup(net2)
+    # separate forwards
+    ya = fbn.bn_act(net1[0], xa, ra, True)
+    g1.step()
+    yb = fbn.bn_act(net1[0], xb, rb, True)
+    g1.step()
+    torch.autograd.backward([ya, yb], [ga, gb])
+    # stacked
+    xs = torch.cat([xa.detach(), xb.detach()]).contiguous(memory_format=fmt).requires_grad_()
+    rs = torch.cat([ra.detach(), rb.detach()]).contiguous(memory_format=fmt).requires_grad_() if residual else None
+    with fbn.segments(2):
+        ys = fbn.bn_act(net2[0], xs, rs, True)
+    g2.step(2)
+    ys.backward(torch.cat([ga, gb]))
+    assert fbn.stream_status() == 0
+    tol = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(ys.float(), torch.cat([ya, yb]).float(), **tol)
+    torch.testing.assert_close(xs.grad.float(), torch.cat([xa.grad, xb.grad]).float(), **tol)
+    if residual:
+        torch.testing.assert_close(rs.grad.float(), torch.cat([ra.grad, rb.grad]).float(), **tol)
+    torch.testing.assert_close(net2[0].weight.grad, net1[0].weight.grad, rtol=1e-3, atol=1e-2)
+    torch.testing.assert_close(net2[0].bias.grad, net1[0].bias.grad, rtol=1e-3, atol=1e-2)
+    torch.testing.assert_close(net2[0].running_mean, net1[0].running_mean, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(net2[0].running_var, net1[0].running_var, rtol=1e-4, atol=1e-5)
+    assert int(net2[0].num_batches_tracked) == int(net1[0].num_batches_tracked) == 2

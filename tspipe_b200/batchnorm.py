@@ -75,10 +75,11 @@ class DeferredBatchNorm(_BatchNorm):
         self.tracked = 0
 
     def forward(self, input: Tensor) -> Tensor:  # type: ignore[override]
-        if input.is_cuda:
-            from .ops import bn as _bn
-            if _bn.applicable(self, input):
-                return _bn.bn_act(self, input)
+        from .ops import bn as _bn
+        if input.is_cuda and _bn.applicable(self, input):
+            return _bn.bn_act(self, input)
+        if self.training and _bn.current_segments() > 1:
+            return _bn.bn_act(self, input)          # stacked views: one statistics set per view
         if not self.training:
             return F.batch_norm(input, self.running_mean, self.running_var, self.weight, self.bias,
                                 training=False, momentum=0.0, eps=self.eps)
@@ -129,7 +130,11 @@ class BatchNormGroup:
         total = sum(m.num_features for m in self.layers)
         mk = lambda v=0.0: torch.full((total,), v, dtype=torch.float32, device=dev)
         self.running_mean, self.running_var = mk(), mk(1.0)
-        self.sum, self.sum_squares, self.count = mk(), mk(), mk()
+        # accumulators as [quantity][set][channel]: set 0 is the one that gets committed; a forward over several
+        # stacked views (`step(segments=n)`) lets view g accumulate into set g, `total` elements further on
+        self.total, self.max_segments = total, 2
+        self._acc = torch.zeros(3, self.max_segments, total, dtype=torch.float32, device=dev)
+        self.sum, self.sum_squares, self.count = self._acc[0, 0], self._acc[1, 0], self._acc[2, 0]
         self.momentum = mk()
         self.cma = torch.zeros(total, dtype=torch.bool, device=dev)
         self.nbt = torch.zeros(len(self.layers), dtype=torch.int64, device=dev)
@@ -156,13 +161,19 @@ class BatchNormGroup:
         self.any_cma = bool(self.cma.any())
 
     @torch.no_grad()
-    def step(self) -> None:
-        """One partition forward (one micro- or nano-batch) has been tracked."""
+    def step(self, segments: int = 1) -> None:
+        """One partition forward (one micro- or nano-batch) has been tracked.  ``segments`` > 1: the forward ran
+        that many stacked views, each with its own statistics in its own accumulator set; they are tracked one
+        after the other, exactly as separate forwards would have been."""
         if not self.layers or not self.module.training:
             return
-        self.tracked += 1
-        if self.tracked >= self.chunks:
-            self.commit()
+        for g in range(segments):
+            if g > 0:
+                self._acc[:, 0] += self._acc[:, g]
+                self._acc[:, g].zero_()
+            self.tracked += 1
+            if self.tracked >= self.chunks:
+                self.commit()
 
     @torch.no_grad()
     def commit(self) -> None:

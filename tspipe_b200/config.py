@@ -39,7 +39,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True},
 }
 
 

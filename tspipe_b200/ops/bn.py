@@ -23,6 +23,32 @@ def set_enabled(flag: bool) -> None:
     _ENABLED = bool(flag)
 
 
+_SEGMENTS = 1
+
+
+class segments:
+    """``with segments(2): y = net(torch.cat([view_1, view_2]))`` - every BatchNorm reached through :func:`bn_act`
+    normalises each of the ``n`` equal, consecutive groups of rows with that group's own statistics, exactly as
+    ``n`` separate forwards would (autograd records the grouping, the backward needs no context)."""
+
+    def __init__(self, n: int):
+        self.n, self.prev = int(n), 1
+
+    def __enter__(self):
+        global _SEGMENTS
+        self.prev, _SEGMENTS = _SEGMENTS, self.n
+        return self
+
+    def __exit__(self, *exc):
+        global _SEGMENTS
+        _SEGMENTS = self.prev
+        return False
+
+
+def current_segments() -> int:
+    return _SEGMENTS
+
+
 def _as_rows(x: torch.Tensor) -> Optional[Tuple[int, int]]:
     """(M, C) when ``x`` is laid out as a contiguous [M, C] matrix with channels innermost."""
     if x.dim() == 2 and x.is_contiguous():
@@ -69,7 +95,8 @@ def stream_status(reset: bool = False) -> int:
 
 class _BnAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None, pre_sums=None):
+    def forward(ctx, x, weight, bias, residual, relu, eps, fixed, acc_sum, acc_sumsq, acc_count=None, pre_sums=None,
+                segs=1, acc_stride=0):
         m, c = _as_rows(x)
         dt = _f._dt(x)
         L = _lib()
@@ -79,23 +106,24 @@ class _BnAct(torch.autograd.Function):
                 residual = residual.to(x.dtype).contiguous(
                     memory_format=torch.channels_last if x.dim() == 4 else torch.contiguous_format)
         # statistics handed over by the producer of x (a convolution epilogue) replace the statistics pass
-        sums = pre_sums if pre_sums is not None else torch.empty(2 * c, dtype=torch.float32, device=x.device)
-        save = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+        sums = pre_sums if pre_sums is not None else torch.empty(segs * 2 * c, dtype=torch.float32, device=x.device)
+        save = torch.empty(segs * 2 * c, dtype=torch.float32, device=x.device)
         wf = weight.detach() if weight.dtype == torch.float32 else weight.detach().float()
         bf = bias.detach() if bias.dtype == torch.float32 else bias.detach().float()
         with torch.cuda.device(x.device):
             st = _f._stream()
             if fixed is None and pre_sums is None:
-                _f._check(L.tsp_bn_stats(_f._ptr(x), _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums), st),
-                          "tsp_bn_stats")
+                _f._check(L.tsp_bn_stats(_f._ptr(x), _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums),
+                                         _c.c_int(segs), st), "tsp_bn_stats")
                 _f._count(2)
             _f._check(L.tsp_bn_apply(_f._ptr(x), _f._ptr(residual), _f._ptr(y), _f._ptr(sums), _f._ptr(fixed),
                                      _f._ptr(wf), _f._ptr(bf), _f._ptr(save), _f._ptr(acc_sum), _f._ptr(acc_sumsq),
-                                     _f._ptr(acc_count), _c.c_int64(m), _c.c_int(c), _c.c_float(eps), _c.c_int(1 if relu else 0),
-                                     _c.c_int(dt), st), "tsp_bn_apply")
+                                     _f._ptr(acc_count), _c.c_int64(acc_stride), _c.c_int64(m), _c.c_int(c),
+                                     _c.c_float(eps), _c.c_int(1 if relu else 0), _c.c_int(dt), _c.c_int(segs), st),
+                      "tsp_bn_apply")
             _f._count()
         ctx.save_for_backward(x, y if (relu and residual is not None) else None, save, wf, bf)
-        ctx.relu, ctx.has_res, ctx.mc = relu, residual is not None, (m, c)
+        ctx.relu, ctx.has_res, ctx.mc, ctx.segs = relu, residual is not None, (m, c), segs
         ctx.wdtype, ctx.bdtype = weight.dtype, bias.dtype
         ctx.fixed = fixed is not None
         ctx.mark_non_differentiable(sums)
@@ -112,13 +140,14 @@ class _BnAct(torch.autograd.Function):
             dy = dy.to(x.dtype).contiguous(memory_format=fmt)
         dx = torch.empty_like(x)
         dres = torch.empty_like(x) if (ctx.has_res and ctx.relu) else None
-        sums = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+        segs = ctx.segs
+        sums = torch.empty(segs * 2 * c, dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
             st = _f._stream()
             relu = _c.c_int(1 if ctx.relu else 0)
             _f._check(L.tsp_bn_bwd_reduce(_f._ptr(dy), _f._ptr(x), _f._ptr(y), _f._ptr(dres), _f._ptr(save),
                                           _f._ptr(wf), _f._ptr(bf), relu,
-                                          _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums), st),
+                                          _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums), _c.c_int(segs), st),
                       "tsp_bn_bwd_reduce")
             if ctx.fixed:
                 # evaluation statistics are constants: dx = w * rstd * dy'
@@ -128,14 +157,16 @@ class _BnAct(torch.autograd.Function):
             src, mask, relu2 = (dres, None, _c.c_int(0)) if dres is not None else (dy, y, relu)
             _f._check(L.tsp_bn_bwd_apply(_f._ptr(src), _f._ptr(x), _f._ptr(mask), _f._ptr(save), _f._ptr(wf),
                                          _f._ptr(bf), relu2, _f._ptr(sums_for_dx), _f._ptr(dx), _c.c_int64(m), _c.c_int(c), _c.c_int(dt),
-                                         st), "tsp_bn_bwd_apply")
+                                         _c.c_int(segs), st), "tsp_bn_bwd_apply")
             _f._count(3)
+        if segs > 1:
+            sums = sums.view(segs, 2 * c).sum(0)
         db, dw = sums[:c], sums[c:]
         if ctx.has_res:
             gres = dres if dres is not None else dy
         else:
             gres = None
-        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None, None, None
+        return dx, dw.to(ctx.wdtype), db.to(ctx.bdtype), gres, None, None, None, None, None, None, None, None, None
 
 
 def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = False,
@@ -144,12 +175,25 @@ def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: b
     BatchNorm, or :class:`~tspipe_b200.batchnorm.DeferredBatchNorm` whose accumulators are fed by the
     same statistics pass).  ``sums`` = per-channel [sum | sum of squares] of ``x`` when its producer already
     computed them (used in training mode only)."""
+    from ..batchnorm import DeferredBatchNorm
+    segs = _SEGMENTS if (getattr(bn, "training", False) and isinstance(bn, _BatchNorm)) else 1
+    if segs > 1:
+        grouped = (isinstance(bn, DeferredBatchNorm) and bn.group is not None and segs <= bn.group.max_segments
+                   and x.shape[0] % segs == 0 and applicable(bn, x[: x.shape[0] // segs]) and applicable(bn, x))
+        if not grouped:
+            # no kernel support for this case: run the groups one after the other
+            with segments(1):
+                xs = x.chunk(segs)
+                rs = residual.chunk(segs) if residual is not None else [None] * segs
+                return torch.cat([bn_act(bn, xg, rg, relu) for xg, rg in zip(xs, rs)])
+        y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, bn.count,
+                            sums, segs, bn.group.total)
+        return y
     if not applicable(bn, x):
         y = bn(x)
         if residual is not None:
             y = y + residual
         return F.relu(y) if relu else y
-    from ..batchnorm import DeferredBatchNorm
     m, c = _as_rows(x)
     if not bn.training or not bn.track_running_stats and False:
         fixed = torch.cat([bn.running_mean.float(), bn.running_var.float()])

@@ -45,17 +45,17 @@ def weight_matrix(weight: torch.Tensor) -> torch.Tensor:
 
 class _StemConv(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, want_sums):
+    def forward(ctx, x, weight, want_sums, segs):
         n, _, h, w = x.shape
         y = torch.empty((n, 64, h // 2, w // 2), dtype=torch.bfloat16, device=x.device,
                         memory_format=torch.channels_last)
-        sums = torch.zeros(128, dtype=torch.float32, device=x.device) if want_sums else None
+        sums = torch.zeros(segs * 128, dtype=torch.float32, device=x.device) if want_sums else None
         wm = weight_matrix(weight)
         L = _f.lib()
         L.tsp_conv_stem_fwd.restype = _c.c_int
         with torch.cuda.device(x.device):
             code = L.tsp_conv_stem_fwd(_f._ptr(x), _f._ptr(wm), _f._ptr(y), _f._ptr(sums), _c.c_int(n), _c.c_int(h),
-                                       _c.c_int(w), _f._ptr(_gemm._status_word(x.device)), _f._stream())
+                                       _c.c_int(w), _c.c_int(segs), _f._ptr(_gemm._status_word(x.device)), _f._stream())
         _f._check(code, "tsp_conv_stem_fwd")
         _f._count()
         ctx.save_for_backward(x, weight)
@@ -76,12 +76,15 @@ class _StemConv(torch.autograd.Function):
             dx = gi
         if ctx.needs_input_grad[1]:
             dw = gw.to(weight.dtype)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
-def stem_conv(x: torch.Tensor, weight: torch.Tensor, want_sums: bool = True
+def stem_conv(x: torch.Tensor, weight: torch.Tensor, want_sums: bool = True, segments: int = 1
               ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """``(y, sums)``: y = conv2d(x, weight, stride 2, padding 3) in channels-last bf16; ``sums`` = per-channel
-    [sum | sum of squares] of y over all pixels (fp32, 128 values) or None."""
-    y, sums = _StemConv.apply(x, weight, want_sums)
+    [sum | sum of squares] of y over all pixels (fp32, ``[segments][128]`` flattened: one set per group of
+    ``N / segments`` consecutive images) or None."""
+    if x.shape[0] % segments != 0:
+        segments = 1
+    y, sums = _StemConv.apply(x, weight, want_sums, segments)
     return y, (sums if want_sums else None)

@@ -249,6 +249,7 @@ class StageEngine:
         from ..batchnorm import BatchNormGroup
         self.bn_group_online = BatchNormGroup(self.online)
         self.bn_group_target = BatchNormGroup(self.target)
+        self.merge_views = self._can_merge_views(rt)
 
         # flat state ---------------------------------------------------------------------------
         self.flat_online = FlatParams([p for p in self.online.parameters()], self.device, with_grad=True,
@@ -568,6 +569,27 @@ class StageEngine:
             data = prepared[pkey]
         return data
 
+    def _can_merge_views(self, rt: Dict[str, Any]) -> bool:
+        """Single stage, two views, one microbatch: both views of a network go through it as ONE forward (and one
+        backward) over the stacked batch.  Every BatchNorm keeps per-view statistics (``ops.bn.segments``), so the
+        numbers are those of two separate forwards; the kernels are twice as large and half as many, which is
+        what a B200 needs at 128 samples per view.  Requires that all batch-statistics layers are
+        :class:`DeferredBatchNorm` (the only ones that know about stacked views)."""
+        from ..batchnorm import DeferredBatchNorm
+        from torch.nn.modules.batchnorm import _BatchNorm
+        if not (rt.get("merge_views", True) and self.fused and not self.kd and self.topo.pp == 1
+                and self.U == 1 and self.S == 1):
+            return False
+        if len(self.spec.student_views) != 2 or len(self.spec.teacher_views) != 2:
+            return False
+        for net in (self.online, self.target):
+            for m in net.modules():
+                if isinstance(m, _BatchNorm) and not isinstance(m, DeferredBatchNorm):
+                    return False
+                if isinstance(m, (nn.InstanceNorm1d, nn.InstanceNorm2d, nn.InstanceNorm3d)):
+                    continue
+        return True
+
     def _conv_input(self) -> bool:
         """True when both networks start with a convolution under bf16 autocast: the cast that autocast would
         do per network and the channels-last conversion can then be one shared kernel per view."""
@@ -660,8 +682,15 @@ class StageEngine:
         first, last = self.topo.is_first, self.topo.is_last
         module = self.target if teacher else self.online
         n_piece = 1 if teacher else self.S
+        merged = self.merge_views
+        if merged and op.view != 0:
+            return                                  # done together with view 0
         with self._on_compute(), self._prof("compute", op, teacher):
-            if first:
+            if first and merged:
+                both = [self._stage0_input(Op(op.kind, op.batch, v, op.ub), teacher) for v in (0, 1)]
+                data = pt.tree_map_tensors_multi(lambda a, b: torch.cat([a, b]), both[0], both[1])
+                pieces = [(data, None)]
+            elif first:
                 data = self._stage0_input(op, teacher)
                 pieces = [(d, None) for d in ([data] if n_piece == 1 else pt.generic_scatter(data, n_piece))]
             else:
@@ -680,13 +709,14 @@ class StageEngine:
                     x = pt.unflatten(leaves, tree, wrapped)
                 if self.channels_last:
                     x = pt.tree_map_tensors(_to_channels_last, x)
-                if teacher:
-                    y = self._teacher_forward(module, x)
-                    self.bn_group_target.step()
-                else:
-                    with self._amp():
-                        y = module(x)
-                    self.bn_group_online.step()
+                with _bn_segments(2 if merged else 1):
+                    if teacher:
+                        y = self._teacher_forward(module, x)
+                        self.bn_group_target.step(2 if merged else 1)
+                    else:
+                        with self._amp():
+                            y = module(x)
+                        self.bn_group_online.step(2 if merged else 1)
                 outs.append(y)
                 if not teacher:
                     oleaves = pt.flatten(y)[0]
@@ -696,7 +726,15 @@ class StageEngine:
                     stored_out.append(oleaves)
             if not teacher:
                 self.acts[(op.batch, op.view, op.ub)] = _Stored(stored_in, stored_out, gin_idx, gout_idx)
-            if not last:
+            if merged:
+                # the loss sees the two views as two outputs again (halves of the stacked batch)
+                for v in (0, 1):
+                    half = pt.tree_map_tensors(lambda t, v=v: t.chunk(2)[v] if t.dim() > 0 else t, outs[0])
+                    if teacher:
+                        self.t_out.setdefault((op.batch, v), [None] * self.U)[op.ub] = half
+                    else:
+                        self.o_out.setdefault((op.batch, v), [None] * self.U)[op.ub] = [half]
+            elif not last:
                 self._send_forward(op, teacher, outs)
             else:
                 key = (op.batch, op.view)
@@ -817,10 +855,15 @@ class StageEngine:
     def _backward(self, op: Op) -> None:
         b, v, k = op.batch, op.view, op.ub
         ub, piece = divmod(k, self.S)
+        if self.merge_views and v != 0:
+            return                                  # done together with view 0
         st = self.acts[(b, v, ub)]
         with self._on_compute(), self._prof("backward", op):
             outs = [st.outputs[piece][i] for i in st.grad_out_idx]
-            if self.topo.is_last:
+            if self.merge_views:
+                g0, g1 = self.out_grads.pop((b, 0, k)), self.out_grads.pop((b, 1, k))
+                grads = [torch.cat([a, c]) for a, c in zip(g0, g1)]
+            elif self.topo.is_last:
                 grads = self.out_grads.pop((b, v, k))
             else:
                 grads = self._recv_backward(op)
@@ -923,6 +966,11 @@ class StageEngine:
                 link.flush()
         if self.cuda:
             self.compute.synchronize()
+
+
+def _bn_segments(n: int):
+    from ..ops import bn as _bn
+    return _bn.segments(n)
 
 
 def _to_conv_input(t: torch.Tensor) -> torch.Tensor:

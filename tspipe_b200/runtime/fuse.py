@@ -34,7 +34,9 @@ class FusedSequential(nn.Sequential):
             nxt = mods[i + 1] if i + 1 < n else None
             if _conv.is_stem_conv(m) and _conv.eligible(x) and torch.is_autocast_enabled():
                 bn_next = isinstance(nxt, _BatchNorm) and nxt.training
-                y, sums = _conv.stem_conv(x, m.weight, want_sums=bn_next)
+                segs = _bn.current_segments() if x.shape[0] % _bn.current_segments() == 0 else 1
+                bn_next = bn_next and (segs == _bn.current_segments())
+                y, sums = _conv.stem_conv(x, m.weight, want_sums=bn_next, segments=segs)
                 if bn_next and _bn.applicable(nxt, y):
                     relu = i + 2 < n and isinstance(mods[i + 2], nn.ReLU)
                     x = _bn.bn_act(nxt, y, relu=relu, sums=sums)

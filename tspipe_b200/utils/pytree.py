@@ -35,6 +35,15 @@ def tree_map_tensors(fn: Callable[[torch.Tensor], Any], obj: Any) -> Any:
     return TSPipeModelOutput(out, None) if wrapped else out
 
 
+def tree_map_tensors_multi(fn: Callable[..., Any], first: Any, *rest: Any) -> Any:
+    """``fn(leaf_of_first, leaf_of_rest_0, ...)`` on the tensor leaves of equally structured pytrees; other
+    leaves are taken from ``first``."""
+    leaves, spec, wrapped = flatten(first)
+    others = [flatten(r)[0] for r in rest]
+    out = [fn(l, *[o[i] for o in others]) if isinstance(l, torch.Tensor) else l for i, l in enumerate(leaves)]
+    return unflatten(out, spec, wrapped)
+
+
 def tensors_of(obj: Any) -> List[torch.Tensor]:
     return [x for x in pytree.tree_leaves(unwrap(obj)) if isinstance(x, torch.Tensor)]
 
