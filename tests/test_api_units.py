@@ -189,3 +189,20 @@ def test_efficientnet_sequential_equals_module_and_logits_loss():
     l = logits_kd(s, t, torch.tensor([0, 1, 2, 3]), extra_args=Namespace(lambda_kd=0.5))
     l.backward()
     assert s.grad is not None and l.item() > 0
+
+
+def test_vit_convolution_stem_variant():
+    """MoCo-v3's ``vit_conv_*`` models: 4 x (conv3x3/2 + BN + ReLU) + 1x1 projection as patch embedding, one
+    transformer block fewer, default initialisation of the stem."""
+    import torch
+    from tspipe_b200.models.vit import CONFIGS, ConvStem, moco_vit_networks
+    assert CONFIGS["vit_conv_base"].depth == 11 and CONFIGS["vit_conv_small"].depth == 11
+    base, momentum, pred = moco_vit_networks("vit_conv_tiny_test", dim=16, mlp_dim=32)
+    stem = next(iter(base.children()))
+    assert isinstance(stem, ConvStem)
+    convs = [m for m in stem.proj if isinstance(m, torch.nn.Conv2d)]
+    assert [c.out_channels for c in convs] == [8, 16, 32, 64, 64] and convs[-1].kernel_size == (1, 1)
+    assert all(torch.equal(a, b) for a, b in zip(base.state_dict().values(), momentum.state_dict().values()))
+    x = torch.randn(4, 3, 32, 32)
+    assert stem(x).shape == (4, 4, 64)
+    assert pred(base(x)).shape == (4, 16)

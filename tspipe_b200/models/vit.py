@@ -40,6 +40,7 @@ class ViTConfig:
     mlp_ratio: float = 4.0
     eps: float = 1e-6
     drop: float = 0.0
+    conv_stem: bool = False      # patch embedding by a 4-layer 3x3/2 convolution stem instead of one 16x16/16 conv
 
 
 CONFIGS = {
@@ -47,7 +48,11 @@ CONFIGS = {
     "vit_base": ViTConfig(embed_dim=768, depth=12, num_heads=12),
     "vit_large": ViTConfig(embed_dim=1024, depth=24, num_heads=16),
     "vit_huge": ViTConfig(embed_dim=1280, depth=32, num_heads=16, patch_size=14),
+    # convolution-stem variants, one transformer block fewer (`benchmarks/moco-v3/vits.py:210-225`)
+    "vit_conv_small": ViTConfig(embed_dim=384, depth=11, num_heads=12, conv_stem=True),
+    "vit_conv_base": ViTConfig(embed_dim=768, depth=11, num_heads=12, conv_stem=True),
     "vit_tiny_test": ViTConfig(img_size=32, patch_size=8, embed_dim=64, depth=2, num_heads=4),
+    "vit_conv_tiny_test": ViTConfig(img_size=32, patch_size=16, embed_dim=64, depth=2, num_heads=4, conv_stem=True),
 }
 
 
@@ -61,6 +66,25 @@ class PatchEmbed(nn.Module):
         super().__init__()
         self.grid = cfg.img_size // cfg.patch_size
         self.proj = nn.Conv2d(in_chans, cfg.embed_dim, cfg.patch_size, stride=cfg.patch_size)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.proj(x).flatten(2).transpose(1, 2)
+
+
+class ConvStem(nn.Module):
+    """Patch embedding as four ``Conv 3x3 / 2 -> BatchNorm -> ReLU`` layers (widths ``dim/8 .. dim``) and a 1x1
+    projection: total stride 16 (`benchmarks/moco-v3/vits.py:91-126`)."""
+
+    def __init__(self, cfg: ViTConfig, in_chans: int = 3):
+        super().__init__()
+        assert cfg.patch_size == 16 and cfg.embed_dim % 8 == 0, "the convolution stem has stride 16"
+        self.grid = cfg.img_size // cfg.patch_size
+        layers, cin, cout = [], in_chans, cfg.embed_dim // 8
+        for _ in range(4):
+            layers += [nn.Conv2d(cin, cout, 3, stride=2, padding=1, bias=False), nn.BatchNorm2d(cout), nn.ReLU()]
+            cin, cout = cout, cout * 2
+        layers.append(nn.Conv2d(cin, cfg.embed_dim, 1))
+        self.proj = nn.Sequential(*layers)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.proj(x).flatten(2).transpose(1, 2)
@@ -144,7 +168,7 @@ def sincos_2d(grid: int, dim: int, temperature: float = 10000.0) -> torch.Tensor
 def vit_trunk_children(cfg: ViTConfig, moco_init: bool = True, stop_grad_conv1: bool = False
                        ) -> "OrderedDict[str, nn.Module]":
     ch: "OrderedDict[str, nn.Module]" = OrderedDict()
-    pe = PatchEmbed(cfg)
+    pe = ConvStem(cfg) if cfg.conv_stem else PatchEmbed(cfg)
     n_tok = pe.grid * pe.grid + 1
     ch["patch_embed"] = pe
     ch["cls_token"] = ClsToken(cfg.embed_dim)
@@ -165,12 +189,13 @@ def vit_trunk_children(cfg: ViTConfig, moco_init: bool = True, stop_grad_conv1: 
         nn.init.normal_(ch["cls_token"].cls_token, std=1e-6)
         with torch.no_grad():
             ch["pos_embed"].pos_embed.copy_(sincos_2d(pe.grid, cfg.embed_dim))
-        val = math.sqrt(6.0 / float(3 * cfg.patch_size * cfg.patch_size + cfg.embed_dim))
-        nn.init.uniform_(pe.proj.weight, -val, val)
-        nn.init.zeros_(pe.proj.bias)
-        if stop_grad_conv1:
-            pe.proj.weight.requires_grad = False
-            pe.proj.bias.requires_grad = False
+        if isinstance(pe, PatchEmbed):       # the convolution stem keeps its default initialisation
+            val = math.sqrt(6.0 / float(3 * cfg.patch_size * cfg.patch_size + cfg.embed_dim))
+            nn.init.uniform_(pe.proj.weight, -val, val)
+            nn.init.zeros_(pe.proj.bias)
+            if stop_grad_conv1:
+                pe.proj.weight.requires_grad = False
+                pe.proj.bias.requires_grad = False
     else:
         nn.init.trunc_normal_(ch["pos_embed"].pos_embed, std=0.02)
         nn.init.trunc_normal_(ch["cls_token"].cls_token, std=0.02)
