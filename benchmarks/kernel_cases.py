@@ -9,6 +9,7 @@
     python benchmarks/kernel_cases.py ln        # LayerNorm fwd/bwd on [512*197, 768]
     python benchmarks/kernel_cases.py gemm      # tcgen05 GEMM 8192 x 3072 x 768
     python benchmarks/kernel_cases.py infonce   # MoCo InfoNCE forward + backward, 4096 x 256
+    python benchmarks/kernel_cases.py attn      # ViT-B attention forward (tcgen05 flash-style kernel)
 
 Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2 where DRAM figures
 matter), runs the op a handful of times and prints CUDA-event timings with the achieved bandwidth.
@@ -213,12 +214,36 @@ def case_infonce():
         logits = F.normalize(q, dim=1) @ F.normalize(k, dim=1).t() / temp
         (F.cross_entropy(logits, torch.arange(n, device=dev)) * 2 * temp).backward()
 
-    t, tr = _time(ours, n=10), _time(ref, n=10)
+    t = _time(ours, n=10)
+    gemm.set_fused_nce(False)
+    tu = _time(ours, n=10)
+    gemm.set_fused_nce(True)
+    tr = _time(ref, n=10)
     gemm.check_status()
-    flops = 2 * 2 * n * n * d          # logits + dq
-    print(f"info_nce fwd+bwd [{n},{d}]: {t:8.1f} us  ({flops / t / 1e6:6.1f} TFLOP/s on the two GEMMs)   library ops: {tr:8.1f} us")
+    flops = 2 * 2 * n * n * d          # scores + weighted sum of keys
+    print(f"info_nce fwd+bwd [{n},{d}]: fused attention-style kernel {t:7.1f} us ({flops / t / 1e6:6.1f} TFLOP/s incl. "
+          f"normalisation kernels) | logits GEMM + CE kernel {tu:7.1f} us | library ops {tr:7.1f} us")
+
+
+def case_attn():
+    """ViT-B attention forward, batch 256 x 12 heads x 197 tokens x 64: tcgen05 kernel against the library."""
+    import torch.nn.functional as F
+    from tspipe_b200.ops import attention, gemm
+    dev = torch.device("cuda")
+    b, h, n, dh = 256, 12, 197, 64
+    qkv = torch.randn(b, n, 3, h, dh, device=dev).bfloat16()
+    q, k, v = qkv.permute(2, 0, 3, 1, 4)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    with torch.no_grad():
+        t = _time(lambda: attention.flash_fwd(q, k, v), n=10, flush=flush)
+        tr = _time(lambda: F.scaled_dot_product_attention(q, k, v), n=10, flush=flush)
+    gemm.check_status()
+    flops = 4 * b * h * n * n * dh
+    byts = 4 * b * h * n * dh * 2
+    print(f"attention fwd [{b},{h},{n},{dh}]: {t:7.1f} us ({flops / t / 1e6:6.1f} TFLOP/s, {byts / t / 1e6:5.2f} TB/s) | "
+          f"library {tr:7.1f} us")
 
 
 if __name__ == "__main__":
     {"bn": case_bn, "bn_r50": case_bn_r50, "stem": case_stem, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
-     "infonce": case_infonce}[sys.argv[1]]()
+     "infonce": case_infonce, "attn": case_attn}[sys.argv[1]]()

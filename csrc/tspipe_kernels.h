@@ -84,6 +84,12 @@ int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, i
 int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, int m, int k,
                                 int lda, int ldb, int ldc, int out_dtype, int* status, cudaStream_t stream);
 
+// ---- attn_tcgen05.cu ----------------------------------------------------------------------------------------------
+int tsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int heads, int nq, int nk,
+                 int d, int dv, const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                 const int64_t* o_strides, float scale, float fixed_max, int use_fixed_max, int out_dtype, int* status,
+                 cudaStream_t stream);
+
 // ---- conv_stem_tcgen05.cu -----------------------------------------------------------------------------------------
 int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int segs,
                       int* status, cudaStream_t stream);

@@ -4,15 +4,81 @@ The reference models run it unfused - two batched GEMMs, a softmax and a dropout
 (timm ``Attention`` in `benchmarks/moco-v3/vits.py`, HF ``BertSelfAttention`` in
 `benchmarks/distilbert/bert.py`).  Here it is one fused call; ``mask`` is an additive or boolean
 key-padding mask broadcastable to [B, 1, 1, N] / [B, H, N, N].
+
+Forward passes that need no gradient (the teacher / momentum encoder) with head dimension 64 and no mask run on
+the tcgen05 kernel of ``csrc/attn_tcgen05.cu`` (:func:`flash_fwd`); everything else goes to the library's fused
+attention, which also provides the backward.
 """
 from __future__ import annotations
 
-from typing import Optional
+import ctypes as _c
+import math
+from typing import Optional, Tuple
 
 import torch
 import torch.nn.functional as F
 
+_TCGEN05 = True
+
+
+def set_tcgen05(flag: bool) -> None:
+    global _TCGEN05
+    _TCGEN05 = bool(flag)
+
+
+def _strides3(t: torch.Tensor):
+    """(row, head, batch) element strides of a [B, H, N, D] tensor as a ctypes array."""
+    return (_c.c_int64 * 3)(t.stride(2), t.stride(1), t.stride(0))
+
+
+def flash_eligible(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    if not (q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16 and q.dim() == k.dim() == v.dim() == 4):
+        return False
+    d, dv = q.shape[-1], v.shape[-1]
+    if (d, dv) not in ((64, 64), (256, 256)):
+        return False
+    if d == 256 and not (k.data_ptr() == v.data_ptr() and k.stride() == v.stride()):
+        return False
+    if q.shape[0] * q.shape[1] > 65535 or k.shape[2] < 1:
+        return False
+    for t in (q, k, v):
+        if t.stride(-1) != 1 or t.data_ptr() % 16 or any(s % 8 for s in t.stride()[:-1]):
+            return False
+    return True
+
+
+def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+              fixed_max: Optional[float] = None, out_dtype: torch.dtype = torch.bfloat16, want_lse: bool = False
+              ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``(O, lse)`` for bf16 ``q [B, H, Nq, D]``, ``k [B, H, Nk, D]``, ``v [B, H, Nk, Dv]`` (any strides with a
+    contiguous last dimension).  ``O`` is returned as a ``[B, H, Nq, Dv]`` view of a ``[B, Nq, H, Dv]`` buffer, so
+    the usual ``o.transpose(1, 2).reshape(B, Nq, H * Dv)`` is free.  ``fixed_max``: an upper bound of
+    ``scale * q.k`` known in advance (removes the running-maximum rescaling)."""
+    from . import fused as _f
+    from . import gemm as _gemm
+    b, h, nq, d = q.shape
+    nk, dv = k.shape[2], v.shape[3]
+    scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
+    o = torch.empty((b, nq, h, dv), dtype=out_dtype, device=q.device).transpose(1, 2)
+    lse = torch.empty((b * h, nq), dtype=torch.float32, device=q.device) if want_lse else None
+    L = _f.lib()
+    L.tsp_attn_fwd.restype = _c.c_int
+    with torch.cuda.device(q.device):
+        code = L.tsp_attn_fwd(_f._ptr(q), _f._ptr(k), _f._ptr(v), _f._ptr(o), _f._ptr(lse), _c.c_int(b), _c.c_int(h),
+                              _c.c_int(nq), _c.c_int(nk), _c.c_int(d), _c.c_int(dv), _strides3(q), _strides3(k),
+                              _strides3(v), _strides3(o), _c.c_float(scale),
+                              _c.c_float(0.0 if fixed_max is None else float(fixed_max)),
+                              _c.c_int(0 if fixed_max is None else 1), _c.c_int(_f._dt(o)),
+                              _f._ptr(_gemm._status_word(q.device)), _f._stream())
+    _f._check(code, "tsp_attn_fwd")
+    _f._count()
+    return o, (lse.view(b, h, nq) if want_lse else None)
+
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: Optional[torch.Tensor] = None,
               dropout_p: float = 0.0) -> torch.Tensor:
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if _TCGEN05 and mask is None and dropout_p == 0.0 and not needs_grad and q.shape[-1] == 64 \
+            and flash_eligible(q, k, v):
+        return flash_fwd(q, k, v)[0]
     return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=dropout_p)

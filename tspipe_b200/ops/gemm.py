@@ -115,6 +115,8 @@ def info_nce(q: torch.Tensor, k: torch.Tensor, temp: float, k_all: Optional[torc
     qn = F.normalize(q.float(), dim=1)
     kn = F.normalize(keys.detach().float(), dim=1)
     n = q.shape[0]
+    if _fused_nce and k_all is None and label_offset == 0 and q.is_cuda and q.shape[1] == 256 and n >= 128:
+        return _FusedNCE.apply(qn, kn.to(torch.bfloat16), float(temp))
     if q.is_cuda and q.shape[1] % 8 == 0 and q.shape[1] >= 64 and n >= 128 and keys.shape[0] >= 64:
         logits = _ScaledLogits.apply(qn, kn, 1.0 / temp)
     else:
@@ -178,6 +180,38 @@ def info_nce_replicas(q: torch.Tensor, k: torch.Tensor, temp: float):
     logits = _GatheredLogits.apply(qn, views, table, n, kn)
     labels = torch.arange(n, device=q.device) + n * ctx.topo.replica
     return _f.cross_entropy(logits, labels) * (2 * temp)
+
+
+_fused_nce = True
+
+
+def set_fused_nce(on: bool) -> None:
+    """Contrastive loss through the fused attention kernel (no N x N logits in memory) when it applies."""
+    global _fused_nce
+    _fused_nce = bool(on)
+
+
+class _FusedNCE(torch.autograd.Function):
+    """``2T * mean_i(logsumexp_j(q_i.k_j / T) - q_i.k_i / T)`` for unit-norm rows, forward and backward from ONE
+    pass of the fused attention kernel with V = K: ``lse`` gives the loss, ``O_i = sum_j p_ij k_j`` the gradient
+    ``dL/dq_i = 2/N (O_i - k_i)``.  Cosine logits are bounded by 1/T, so the kernel runs without rescaling."""
+
+    @staticmethod
+    def forward(ctx, qn, kn16, temp):
+        from .attention import flash_fwd
+        n, d = qn.shape
+        q16 = qn.to(torch.bfloat16)
+        o, lse = flash_fwd(q16.view(1, 1, n, d), kn16.view(1, 1, -1, d), kn16.view(1, 1, -1, d), scale=1.0 / temp,
+                           fixed_max=1.0 / temp, out_dtype=torch.float32, want_lse=True)
+        pos = (q16.float() * kn16[:n].float()).sum(1) / temp
+        ctx.save_for_backward(o.reshape(n, d), kn16)
+        ctx.n, ctx.qdtype = n, qn.dtype
+        return (lse.view(n) - pos).mean() * (2 * temp)
+
+    @staticmethod
+    def backward(ctx, g):
+        o, kn16 = ctx.saved_tensors
+        return ((o - kn16[: ctx.n].float()) * (g * 2.0 / ctx.n)).to(ctx.qdtype), None, None
 
 
 class _ScaledLogits(torch.autograd.Function):
