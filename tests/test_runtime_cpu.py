@@ -144,6 +144,31 @@ def test_ssl_momentum_pipeline_matches_oracle(pp, n_ub, split, skip, gpipe):
         torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)
 
 
+def _merge_rank(rank, world, merge, n_steps):
+    cfg = {"model_split": {"online": [8], "target": [5]},
+           "runtime": {"num_ubatch": 1, "bwd_split": 1, "backend": "gloo", "timeout_s": 60, "merge_views": merge},
+           "train": {"deferred_batch_norm": True}}
+    out = _ssl_rank(rank, world, cfg, n_steps)
+    return out
+
+
+def test_stacked_views_on_a_single_stage_equal_one_forward_per_view():
+    """Single stage, one microbatch: both views of a network run as ONE stacked forward/backward with per-view
+    BatchNorm statistics.  Losses, parameters and running statistics equal those of one forward per view and the
+    losses equal the oracle's."""
+    n_steps = 6
+    merged = run_ranks(_merge_rank, 1, True, n_steps)[0]
+    plain = run_ranks(_merge_rank, 1, False, n_steps)[0]
+    ref_losses, _, _ = _ssl_oracle(n_steps, 1, 1)
+    torch.testing.assert_close(torch.tensor(merged[0]), torch.tensor(ref_losses), rtol=2e-5, atol=1e-6)
+    torch.testing.assert_close(torch.tensor(merged[0]), torch.tensor(plain[0]), rtol=1e-5, atol=1e-6)
+    for got, want in ((merged[1], plain[1]), (merged[2], plain[2])):
+        for j in want:
+            assert list(got[j]) == list(want[j])
+            for k in want[j]:
+                torch.testing.assert_close(got[j][k], want[j][k], rtol=1e-5, atol=1e-6, msg=k)
+
+
 # ---------------------------------------------------------------------------------------------
 def _moco_models():
     torch.manual_seed(3)

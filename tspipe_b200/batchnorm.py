@@ -41,6 +41,7 @@ class DeferredBatchNorm(_BatchNorm):
         self.chunks = chunks
         self.group: Optional["BatchNormGroup"] = None     # set when the partition's statistics are flattened
         self.count: Optional[Tensor] = None
+        self._slice = slice(0, num_features)              # this layer's channels inside the group's flat buffers
 
     def _check_input_dim(self, input: Tensor) -> None:
         if input.dim() < 2:
@@ -52,11 +53,15 @@ class DeferredBatchNorm(_BatchNorm):
         ``_mb_var`` over ``n`` elements per channel) into the mini-batch accumulators."""
         mean = self._mb_mean
         var_b = self._mb_var * ((n - 1) / n) if n > 1 else torch.zeros_like(self._mb_var)
+        if self.group is not None:
+            from .ops import bn as _bn
+            acc = self.group._acc[:, _bn.current_segment_index(), self._slice]     # this view's accumulator set
+            acc[0].add_(mean, alpha=n)
+            acc[1].add_((var_b + mean * mean), alpha=n)
+            acc[2].add_(n)
+            return False
         self.sum.add_(mean, alpha=n)
         self.sum_squares.add_((var_b + mean * mean), alpha=n)
-        if self.group is not None:
-            self.count.add_(n)
-            return False
         self.counter += n
         self.tracked += 1
         return self.tracked == self.chunks
@@ -151,6 +156,7 @@ class BatchNormGroup:
                 self.nbt[i] = m.num_batches_tracked
                 m._buffers["num_batches_tracked"] = self.nbt[i]
                 m.count = self.count[sl]
+                m._slice = sl
                 if m.momentum is None:
                     self.cma[sl] = True
                 else:

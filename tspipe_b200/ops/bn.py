@@ -49,6 +49,13 @@ def current_segments() -> int:
     return _SEGMENTS
 
 
+_SEG_INDEX = 0      # which view a BatchNorm call belongs to while stacked views are run one after the other
+
+
+def current_segment_index() -> int:
+    return _SEG_INDEX
+
+
 def _as_rows(x: torch.Tensor) -> Optional[Tuple[int, int]]:
     """(M, C) when ``x`` is laid out as a contiguous [M, C] matrix with channels innermost."""
     if x.dim() == 2 and x.is_contiguous():
@@ -182,10 +189,18 @@ def bn_act(bn, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: b
                    and x.shape[0] % segs == 0 and applicable(bn, x[: x.shape[0] // segs]) and applicable(bn, x))
         if not grouped:
             # no kernel support for this case: run the groups one after the other
+            global _SEG_INDEX
             with segments(1):
                 xs = x.chunk(segs)
                 rs = residual.chunk(segs) if residual is not None else [None] * segs
-                return torch.cat([bn_act(bn, xg, rg, relu) for xg, rg in zip(xs, rs)])
+                outs = []
+                try:
+                    for g, (xg, rg) in enumerate(zip(xs, rs)):
+                        _SEG_INDEX = g               # the deferred accumulators of view g
+                        outs.append(bn_act(bn, xg, rg, relu))
+                finally:
+                    _SEG_INDEX = 0
+                return torch.cat(outs)
         y, _ = _BnAct.apply(x, bn.weight, bn.bias, residual, relu, bn.eps, None, bn.sum, bn.sum_squares, bn.count,
                             sums, segs, bn.group.total)
         return y

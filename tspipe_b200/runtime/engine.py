@@ -577,8 +577,7 @@ class StageEngine:
         :class:`DeferredBatchNorm` (the only ones that know about stacked views)."""
         from ..batchnorm import DeferredBatchNorm
         from torch.nn.modules.batchnorm import _BatchNorm
-        if not (rt.get("merge_views", True) and self.fused and not self.kd and self.topo.pp == 1
-                and self.U == 1 and self.S == 1):
+        if not (rt.get("merge_views", True) and not self.kd and self.topo.pp == 1 and self.U == 1 and self.S == 1):
             return False
         if len(self.spec.student_views) != 2 or len(self.spec.teacher_views) != 2:
             return False
