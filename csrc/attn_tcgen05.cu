@@ -155,9 +155,16 @@ struct Cfg {
   static constexpr int kOCol = 2 * BN;                        // S buffers at columns 0 and BN, O behind them
 };
 
+// K may be the row-wise concatenation of several equally sized buffers (one per GPU): key tile j then comes from
+// source (j * BN) / rows_per_src, which this CTA reads with its own TMA load (local or peer memory alike).
+constexpr int kMaxKSources = 8;
+struct KMaps {
+  CUtensorMap m[kMaxKSources];
+};
+
 template <int D, int DV, int BN, bool SAME, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ KMaps kmaps, int rows_per_src,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
                 float* __restrict__ lse, int nq, int nk, int heads, float scale, float fixed_max, int use_fixed_max,
                 int* __restrict__ status) {
@@ -197,7 +204,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(o_final, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_q) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&kmaps.m[0]) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_v) : "memory");
   }
   if (warp == 1) {
@@ -223,8 +230,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         uint8_t* k_dst = kv_s + s * (C::kKBytes + C::kVBytes);
         uint8_t* v_dst = k_dst + C::kKBytes;
         mbar_expect_tx(kv_full + s, (uint32_t)(C::kKBytes + C::kVBytes));
+        const int src = (j * BN) / rows_per_src, row_in_src = j * BN - src * rows_per_src;
         for (int kb = 0; kb < D / 64; ++kb)
-          tma_load_4d(k_dst + kb * (BN * 128), &tmap_k, kv_full + s, kb * 64, j * BN, head, bat);
+          tma_load_4d(k_dst + kb * (BN * 128), &kmaps.m[src], kv_full + s, kb * 64, row_in_src, head, bat);
         if (!SAME) {
           for (int cb = 0; cb < DV / 64; ++cb)
             tma_load_4d(v_dst + cb * (BN * 128), &tmap_v, kv_full + s, cb * 64, j * BN, head, bat);
@@ -447,15 +455,19 @@ bool make_map4(CUtensorMap* map, const void* ptr, int batch, int heads, int rows
 struct Strides { int64_t ld, hs, bs; };
 
 template <int D, int DV, int BN, bool SAME, typename OutT>
-int launch(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int heads, int nq, int nk,
-           Strides sq, Strides sk, Strides sv, Strides so, float scale, float fixed_max, int use_fixed_max, int* status,
-           cudaStream_t stream) {
+int launch(const void* q, void* const* k_srcs, int n_src, const void* v, void* o, float* lse, int batch, int heads, int nq,
+           int nk, Strides sq, Strides sk, Strides sv, Strides so, float scale, float fixed_max, int use_fixed_max,
+           int* status, cudaStream_t stream) {
   using C = Cfg<D, DV, BN, SAME>;
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tv, to;
+  KMaps tk;
   constexpr bool f32 = sizeof(OutT) == 4;
+  const int rows_per_src = n_src == 1 ? nk : nk / n_src;
+  for (int i = 0; i < kMaxKSources; ++i)
+    if (!make_map4(&tk.m[i], k_srcs[i < n_src ? i : 0], batch, heads, rows_per_src, D, sk.ld, sk.hs, sk.bs, 64, BN, false))
+      return -6;
   if (!make_map4(&tq, q, batch, heads, nq, D, sq.ld, sq.hs, sq.bs, 64, BM, false) ||
-      !make_map4(&tk, k, batch, heads, nk, D, sk.ld, sk.hs, sk.bs, 64, BN, false) ||
-      !make_map4(&tv, v, batch, heads, nk, DV, sv.ld, sv.hs, sv.bs, 64, BN, false) ||
+      !make_map4(&tv, v, batch, heads, SAME ? rows_per_src : nk, DV, sv.ld, sv.hs, sv.bs, 64, BN, false) ||
       !make_map4(&to, o, batch, heads, nq, DV, so.ld, so.hs, so.bs, f32 ? 32 : 64, 32, f32))
     return -6;
   auto kern = attn_fwd_kernel<D, DV, BN, SAME, OutT>;
@@ -469,8 +481,8 @@ int launch(const void* q, const void* k, const void* v, void* o, float* lse, int
     attr_set[dev] = true;
   }
   dim3 grid((nq + BM - 1) / BM, batch * heads);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, nq, nk, heads, scale, fixed_max, use_fixed_max,
-                                                  status);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, n_src == 1 ? nk + BN : rows_per_src, tv, to, lse, nq, nk, heads,
+                                                  scale, fixed_max, use_fixed_max, status);
   return TSP_LAUNCH_CHECK();
 }
 
@@ -499,13 +511,31 @@ int tsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
   const bool bf16 = out_dtype == TSP_DTYPE_BF16;
   const int oesz = bf16 ? 2 : 4;
   if ((so.ld * oesz) % 16 != 0 || (so.hs * oesz) % 16 != 0 || (so.bs * oesz) % 16 != 0) return -3;
-#define TSP_ATTN_ARGS q, k, v, o, lse, batch, heads, nq, nk, sq, sk, sv, so, scale, fixed_max, use_fixed_max, status, stream
+  void* const srcs[1] = {const_cast<void*>(k)};
+#define TSP_ATTN_ARGS q, srcs, 1, v, o, lse, batch, heads, nq, nk, sq, sk, sv, so, scale, fixed_max, use_fixed_max, status, stream
   if (d == 64 && dv == 64)
     return bf16 ? launch<64, 64, 128, false, __nv_bfloat16>(TSP_ATTN_ARGS) : launch<64, 64, 128, false, float>(TSP_ATTN_ARGS);
   if (d == 256 && dv == 256 && k == v && sk.ld == sv.ld && sk.hs == sv.hs && sk.bs == sv.bs)
     return bf16 ? launch<256, 256, 64, true, __nv_bfloat16>(TSP_ATTN_ARGS) : launch<256, 256, 64, true, float>(TSP_ATTN_ARGS);
 #undef TSP_ATTN_ARGS
   return -3;
+}
+
+// Contrastive-loss form with the keys of `n_src` replicas read in place: Q [nq][256] bf16 (pitch 256), K = V = the
+// row-wise concatenation of k_srcs[0..n_src) (each [rows_per_src][256] bf16, pitch 256; pointers may be peer
+// memory - every CTA fetches its own tiles with plain TMA loads).  O [nq][256] fp32, lse [nq].  rows_per_src % 64 == 0.
+int tsp_attn_nce_gathered(const void* q, void* const* k_srcs, int n_src, int rows_per_src, void* o, float* lse, int nq,
+                          float scale, float fixed_max, int* status, cudaStream_t stream) {
+  if (nq <= 0 || n_src <= 0 || rows_per_src <= 0) return 0;
+  if (n_src > kMaxKSources || rows_per_src % 64 != 0) return -3;
+  if ((((uintptr_t)q | (uintptr_t)o) & 15) != 0) return -2;
+  for (int i = 0; i < n_src; ++i)
+    if (((uintptr_t)k_srcs[i] & 15) != 0) return -2;
+  const int nk = n_src * rows_per_src;
+  const Strides sq = {256, (int64_t)nq * 256, (int64_t)nq * 256};
+  const Strides sk = {256, (int64_t)rows_per_src * 256, (int64_t)rows_per_src * 256};
+  return launch<256, 256, 64, true, float>(q, k_srcs, n_src, k_srcs[0], o, lse, 1, 1, nq, nk, sq, sk, sk, sq, scale,
+                                           fixed_max, 1, status, stream);
 }
 
 }  // extern "C"

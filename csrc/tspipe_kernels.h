@@ -90,6 +90,9 @@ int tsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                  const int64_t* o_strides, float scale, float fixed_max, int use_fixed_max, int out_dtype, int* status,
                  cudaStream_t stream);
 
+int tsp_attn_nce_gathered(const void* q, void* const* k_srcs, int n_src, int rows_per_src, void* o, float* lse, int nq,
+                          float scale, float fixed_max, int* status, cudaStream_t stream);
+
 // ---- conv_stem_tcgen05.cu -----------------------------------------------------------------------------------------
 int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int segs,
                       int* status, cudaStream_t stream);

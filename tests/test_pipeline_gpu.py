@@ -73,12 +73,12 @@ def test_byol_two_stage_pipeline_with_cross_gpu_momentum_update():
         torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-5)
 
 
-def _moco_models():
+def _moco_models(dim=64):
     from tspipe_b200.models.mlp import mlp_sequential
     torch.manual_seed(3)
-    online = mlp_sequential([32, 64, 64])
+    online = mlp_sequential([32, 64, dim])
     target = copy.deepcopy(online)
-    predictor = nn.Sequential(nn.Linear(64, 64), nn.Tanh(), nn.Linear(64, 64))
+    predictor = nn.Sequential(nn.Linear(dim, 64), nn.Tanh(), nn.Linear(64, dim))
     return online, target, predictor
 
 
@@ -87,11 +87,11 @@ def _moco_batches(n):
     return [(torch.randn(256, 32, generator=g), torch.randn(256, 32, generator=g)) for _ in range(n)]
 
 
-def _moco_rank(rank, world, n_steps):
+def _moco_rank(rank, world, n_steps, dim=64):
     import torch.distributed as dist
     from tspipe_b200 import TSPipe
     from tspipe_b200.losses import ema_update, moco_loss
-    online, target, predictor = _moco_models()
+    online, target, predictor = _moco_models(dim)
     opt = torch.optim.SGD(list(online.parameters()) + list(predictor.parameters()), lr=0.2)
     cfg = {"model_split": {"online": [6], "target": [3]},
            "runtime": {"num_ubatch": 2, "bwd_split": 1, "dtype": "fp32", "dp_replicas": 2, "timeout_s": 120},
@@ -111,11 +111,14 @@ def _moco_rank(rank, world, n_steps):
     return losses
 
 
-def test_moco_replicas_gather_keys_through_peer_memory_and_tcgen05_logits():
+@pytest.mark.parametrize("dim", [64, 256])
+def test_moco_replicas_gather_keys_through_peer_memory_and_tcgen05_logits(dim):
+    """dim 64: gathered-key tcgen05 GEMM + CE kernel; dim 256: the fused attention-style kernel that streams key
+    tiles from both replicas' buffers and never writes the logits."""
     from tspipe_b200.losses import ema_update, moco_loss
     from tspipe_b200.oracle import DelayedTeacherOracle
     n_steps = 3
-    online, target, predictor = _moco_models()
+    online, target, predictor = _moco_models(dim)
     full = nn.Sequential(*list(online.children()), *list(predictor.children()))
     opt = torch.optim.SGD(full.parameters(), lr=0.2)
     orc = DelayedTeacherOracle(full, target, opt, moco_loss, ema_update, 0.9, kd=False, n_ubatch=4, bwd_split=1,
@@ -124,7 +127,7 @@ def test_moco_replicas_gather_keys_through_peer_memory_and_tcgen05_logits():
     f = orc.update_fn
     orc.update_fn = lambda m, on, tg: f(m, on[:n_t], tg)
     ref = [orc.step(a, b) for a, b in _moco_batches(n_steps)]
-    out = run_ranks(_moco_rank, 2, n_steps)
+    out = run_ranks(_moco_rank, 2, n_steps, dim)
     mean = [(x + y) / 2 for x, y in zip(out[0], out[1])]
     torch.testing.assert_close(torch.tensor(mean), torch.tensor(ref), rtol=2e-2, atol=2e-2)   # bf16 logits
 

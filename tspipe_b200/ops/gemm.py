@@ -171,6 +171,13 @@ def info_nce_replicas(q: torch.Tensor, k: torch.Tensor, temp: float):
     n, d = q.shape
     if ctx is None or ctx.topo.dp <= 1 or not q.is_cuda or d % 8 or d < 64 or n % 128:
         return None
+    if _fused_nce and d == 256 and ctx.topo.dp <= 8:
+        # attention-style kernel: every CTA streams key tiles from all replicas' buffers; no logits in memory
+        kn16 = F.normalize(k.detach().float(), dim=1).to(torch.bfloat16).contiguous()
+        ex = exchange_for(kn16, "moco_keys_bf16")
+        if ex is not None:
+            views, _ = ex.publish(kn16)
+            return _FusedNCEGathered.apply(F.normalize(q.float(), dim=1), kn16, views, float(temp))
     kn = (F.normalize(k.detach().float(), dim=1) * (1.0 / temp)).to(torch.bfloat16).contiguous()
     ex = exchange_for(kn, "moco_keys_scaled_bf16")
     if ex is None:
@@ -212,6 +219,36 @@ class _FusedNCE(torch.autograd.Function):
     def backward(ctx, g):
         o, kn16 = ctx.saved_tensors
         return ((o - kn16[: ctx.n].float()) * (g * 2.0 / ctx.n)).to(ctx.qdtype), None, None
+
+
+class _FusedNCEGathered(torch.autograd.Function):
+    """:class:`_FusedNCE` against the keys of ALL replicas, read in place from the GPUs that own them (positives
+    are the local keys: row i of this replica pairs with key ``i + n * replica`` of the concatenation)."""
+
+    @staticmethod
+    def forward(ctx, qn, kn16, views, temp):
+        from ..comm.peer import pointer_table
+        n, d = qn.shape
+        q16 = qn.to(torch.bfloat16).contiguous()
+        o = torch.empty(n, d, dtype=torch.float32, device=qn.device)
+        lse = torch.empty(n, dtype=torch.float32, device=qn.device)
+        L = _f.lib()
+        L.tsp_attn_nce_gathered.restype = _c.c_int
+        with torch.cuda.device(qn.device):
+            code = L.tsp_attn_nce_gathered(_f._ptr(q16), pointer_table(views), _c.c_int(len(views)), _c.c_int(n),
+                                           _f._ptr(o), _f._ptr(lse), _c.c_int(n), _c.c_float(1.0 / temp),
+                                           _c.c_float(1.0 / temp), _f._ptr(_status_word(qn.device)), _f._stream())
+        _f._check(code, "tsp_attn_nce_gathered")
+        _f._count()
+        pos = (q16.float() * kn16.float()).sum(1) / temp
+        ctx.save_for_backward(o, kn16)
+        ctx.n, ctx.qdtype = n, qn.dtype
+        return (lse - pos).mean() * (2 * temp)
+
+    @staticmethod
+    def backward(ctx, g):
+        o, kn16 = ctx.saved_tensors
+        return ((o - kn16.float()) * (g * 2.0 / ctx.n)).to(ctx.qdtype), None, None, None
 
 
 class _ScaledLogits(torch.autograd.Function):
