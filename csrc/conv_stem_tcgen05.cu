@@ -29,7 +29,7 @@ namespace {
 constexpr int kCout = 64;
 constexpr int kK = 160;                   // 147 rounded up to a multiple of 16
 constexpr int kKPad = 192;                // weight matrix row length: three 64-wide k blocks
-constexpr int kAStages = 2;
+constexpr int kAStages = 3;
 constexpr int kABlockBytes = 128 * 128;   // one k block of A: 128 rows x 128 bytes
 constexpr int kAStageBytes = 3 * kABlockBytes;
 constexpr int kBBlockBytes = kCout * 128;
@@ -227,21 +227,32 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       if (p < ow_n) {
         uint8_t* a_stage = a_tiles + s * kAStageBytes;
         const uint32_t row_off = (uint32_t)(p >> 3) * 1024u + (uint32_t)(p & 7) * 128u;
-        const __nv_bfloat16* rows[7];
+        // Patch row kh of this pixel = 21 bf16 starting at byte 12 p + 14 of the ring row: always 2 bytes past a
+        // 4-byte boundary.  Read the 11 aligned words that cover it (lanes 12 bytes apart: conflict-free) and
+        // recombine halves: the k stream (kh * 21 + i) is cut into 32-bit output words with compile-time shuffles.
+        const uint8_t* rows[7];
 #pragma unroll
         for (int kh = 0; kh < 7; ++kh)
-          rows[kh] = reinterpret_cast<const __nv_bfloat16*>(ring + ((ih0 + kh + 16) & (kRingSlots - 1)) * kRowBytes) +
-                     6 * p + 7;
+          rows[kh] = ring + ((ih0 + kh + 16) & (kRingSlots - 1)) * kRowBytes + 12 * p + 12;
+        auto ldw = [&](int kh, int c) -> uint32_t { return *reinterpret_cast<const uint32_t*>(rows[kh] + 4 * c); };
 #pragma unroll
-        for (int q = 0; q < kK / 8; ++q) {          // 16-byte piece q: k = 8q .. 8q+7, all offsets compile-time
+        for (int q = 0; q < kK / 8; ++q) {          // 16-byte piece q: k = 8q .. 8q+7
           uint32_t wd[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int k0 = 8 * q + 2 * e, k1 = k0 + 1;
-            uint32_t lo = 0, hi = 0;
-            if (k0 < 147) lo = *reinterpret_cast<const uint16_t*>(rows[k0 / 21] + (k0 % 21));
-            if (k1 < 147) hi = *reinterpret_cast<const uint16_t*>(rows[k1 / 21] + (k1 % 21));
-            wd[e] = lo | (hi << 16);
+            const int s0 = 8 * q + 2 * e, s1 = s0 + 1;        // stream positions of the two halves
+            uint32_t out = 0;
+            if (s0 < 147) {
+              const int kh0 = s0 / 21, h0 = s0 % 21 + 1;       // halfword index inside the 22-halfword window
+              if (s1 >= 147) {
+                out = ldw(kh0, h0 >> 1) >> 16;                // last element of the patch, zero above
+              } else if (s1 / 21 == kh0) {
+                out = (h0 & 1) ? __funnelshift_r(ldw(kh0, h0 >> 1), ldw(kh0, (h0 >> 1) + 1), 16) : ldw(kh0, h0 >> 1);
+              } else {                                         // last element of row kh0, first of row kh0 + 1
+                out = __byte_perm(ldw(kh0, 10), ldw(kh0 + 1, 0), 0x7632);
+              }
+            }
+            wd[e] = out;
           }
           const int kb = q >> 3, piece = q & 7;
           *reinterpret_cast<uint4*>(a_stage + kb * kABlockBytes + row_off + ((piece ^ (p & 7)) << 4)) =
