@@ -267,6 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row0 = m0 + quarter * 32, row = row0 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kCols) {
+        if (n0 + c0 >= n) break;                  // columns past the matrix edge: nothing to convert or store
         float v[kCols];
         {
           uint32_t r[kCols];

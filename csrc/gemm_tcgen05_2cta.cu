@@ -146,11 +146,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
-template <typename OutT>
+template <typename OutT, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ CUtensorMap tmap_c, int tma_store, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
-                         int* __restrict__ status) {
+                         const __grid_constant__ CUtensorMap tmap_c, int tma_store, OutT* __restrict__ c,
+                         const float* __restrict__ bias, int m, int n, int k, int ldc, int epi,
+                         float* __restrict__ col_sums, int seg_rows, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* store_bufs = tiles + kStages * kStageBytes; // 1024-aligned: the swizzle pattern follows address bits
@@ -261,15 +262,39 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint8_t* my_bufs = store_bufs + quarter * 2 * kStoreBufBytes;
     uint32_t lt = 0, nstore = 0;
     bool ok = true;
+    // STATS: per-column sum and sum of squares of the rounded outputs (the statistics of a BatchNorm that
+    // follows a 1x1 convolution), kept in registers while this warp stays in the same column block and row
+    // group: cs[i] = {sum, sumsq of column 2*lane, sum, sumsq of column 2*lane+1} of 64-column block i.
+    float cs[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { cs[i][0] = cs[i][1] = cs[i][2] = cs[i][3] = 0.f; }
+    int cur_n0 = -1, cur_seg = 0;
+    auto flush_stats = [&]() {
+      if (cur_n0 >= 0) {
+        float* dst = col_sums + (int64_t)cur_seg * 2 * n;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = cur_n0 + 64 * i + 2 * lane;
+          if (col < n) { atomicAdd(dst + col, cs[i][0]); atomicAdd(dst + n + col, cs[i][1]); }
+          if (col + 1 < n) { atomicAdd(dst + col + 1, cs[i][2]); atomicAdd(dst + n + col + 1, cs[i][3]); }
+          cs[i][0] = cs[i][1] = cs[i][2] = cs[i][3] = 0.f;
+        }
+      }
+    };
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
       const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM, n0 = (t / tiles_m) * BN;
       const uint32_t acc = lt & 1, use = lt >> 1;
+      if (STATS) {
+        const int seg = m0 / seg_rows;
+        if (n0 != cur_n0 || seg != cur_seg) { flush_stats(); cur_n0 = n0; cur_seg = seg; }
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3));   // one way out per warp
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row0 = m0 + quarter * 32, row = row0 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += kCols) {
+      // one block of kCols columns; returns false past the matrix edge
+      auto chunk = [&](int c0, float* st) -> bool {
+        if (n0 + c0 >= n) return false;            // columns past the matrix edge: nothing to convert or store
         float v[kCols];
         {
           uint32_t r[kCols];
@@ -318,17 +343,38 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             else asm volatile("cp.async.bulk.commit_group;" ::: "memory");     // keep the group count in step
           }
           ++nstore;
+          if (STATS && st != nullptr) {
+            // column sums of the staged (rounded) block: lane owns columns 2*lane, 2*lane+1; rows past the
+            // matrix edge hold exact zeros (their A rows were zero-filled)
+#pragma unroll 8
+            for (int rr = 0; rr < 32; ++rr) {
+              const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                                     (lane & 3) * 4);
+              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
+              st[0] += f.x; st[1] += f.x * f.x; st[2] += f.y; st[3] += f.y * f.y;
+            }
+          }
         } else if (row < m && col < n) {
           OutT* dst = c + (int64_t)row * ldc + col;
 #pragma unroll
           for (int j = 0; j < kCols; ++j)       // constant indices only: v stays in registers
             if (col + j < n) tsp::st(dst, j, v[j]);
         }
+        return true;
+      };
+      if constexpr (STATS) {
+        static_assert(!STATS || kCols == 64, "column statistics are kept for bf16 outputs");
+        if (chunk(0, cs[0]) && chunk(64, cs[1]) && chunk(128, cs[2])) chunk(192, cs[3]);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kCols)
+          if (!chunk(c0, nullptr)) break;
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty_bar + acc), 0));
     }
+    if (STATS) flush_stats();
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staging buffers are free again
     __syncwarp();
   }
@@ -387,15 +433,16 @@ bool make_store_map(CUtensorMap* map, void* ptr, int rows, int cols, int ld, boo
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename OutT>
+template <typename OutT, bool STATS>
 int launch(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb, int ldc,
-           int epi, int* status, cudaStream_t stream) {
+           int epi, float* col_sums, int seg_rows, int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (!make_map(&ta, a, m, k, lda, BM) || !make_map(&tb, b, n, k, ldb, BN / 2)) return -6;
   CUtensorMap tc = ta;          // placeholder when C cannot be described (the kernel then stores directly)
   const bool aligned_c = (((uintptr_t)c & 15) == 0) && ((ldc * (int)sizeof(OutT)) % 16 == 0);
   const int tma_store = aligned_c && make_store_map(&tc, c, m, n, ldc, sizeof(OutT) == 2) ? 1 : 0;
-  auto kern = gemm_tcgen05_2cta_kernel<OutT>;
+  if (STATS && !tma_store) return -3;           // the statistics are taken from the staged blocks
+  auto kern = gemm_tcgen05_2cta_kernel<OutT, STATS>;
   static bool attr_set[64] = {};
   static int n_sm[64] = {};
   int dev = 0;
@@ -423,7 +470,7 @@ int launch(const void* a, const void* b, void* c, const float* bias, int m, int 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tma_store, (OutT*)c, bias, m, n, k, ldc, epi, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tma_store, (OutT*)c, bias, m, n, k, ldc, epi, col_sums, seg_rows, status);
   return (int)e;
 }
 
@@ -441,8 +488,20 @@ int tsp_gemm_bf16_tn_2cta(const void* a, const void* b, void* c, const float* bi
   if (epi != 0 && bias == nullptr) return -3;
   if ((lda % 8) || (ldb % 8) || (k % 8)) return -3;
   if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
-  if (out_dtype == TSP_DTYPE_BF16) return launch<__nv_bfloat16>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
-  return launch<float>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, status, stream);
+  if (out_dtype == TSP_DTYPE_BF16) return launch<__nv_bfloat16, false>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, nullptr, 1, status, stream);
+  return launch<float, false>(a, b, c, bias, m, n, k, lda, ldb, ldc, epi, nullptr, 1, status, stream);
+}
+
+// C (bf16) = A B^T as above, plus per-column statistics of the rounded result for a BatchNorm that follows:
+// col_sums [segs][2n] fp32 (zeroed by the caller) receives, for each of the `segs` consecutive groups of
+// m / segs rows, the column sums and the column sums of squares.  m / segs must be a multiple of 128; C must be
+// 16-byte aligned with a row pitch that is a multiple of 16 bytes.
+int tsp_gemm_bf16_tn_2cta_stats(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
+                                float* col_sums, int segs, int* status, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (k % 8) || segs < 1 || m % segs != 0 || (m / segs) % 128 != 0) return -3;
+  if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
+  return launch<__nv_bfloat16, true>(a, b, c, nullptr, m, n, k, lda, ldb, ldc, 0, col_sums, m / segs, status, stream);
 }
 
 }  // extern "C"

@@ -79,3 +79,61 @@ def test_stem_conv_statistics_per_group_of_images():
     for g, part in enumerate((yf[:3], yf[3:])):
         torch.testing.assert_close(sums[g, :64], part.sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
         torch.testing.assert_close(sums[g, 64:], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("shape,cout,segs", [((4, 64, 16, 16), 256, 1), ((8, 256, 8, 8), 64, 2), ((2, 512, 16, 8), 1024, 2),
+                                             ((6, 128, 16, 16), 520, 1)])
+def test_conv1x1_gemm_with_batchnorm_statistics(shape, cout, segs):
+    """1 x 1 convolution on the tcgen05 GEMM: output, per-group column statistics and gradients vs F.conv2d."""
+    from tspipe_b200.ops import conv, gemm
+    torch.manual_seed(3)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(shape, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last).requires_grad_()
+    m = nn.Conv2d(shape[1], cout, 1, bias=False).to(dev)
+    assert conv.conv1x1_eligible(m, x, segs)
+    conv.clear_weight_cache()
+    y, sums = conv.conv1x1(x, m.weight, segs)
+    gemm.check_status()
+    xr = x.detach().float().requires_grad_()
+    wr = m.weight.detach().bfloat16().float().requires_grad_()
+    ref = F.conv2d(xr, wr)
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    yf = y.float()
+    sums = sums.view(segs, 2, cout)
+    for g, part in enumerate(yf.chunk(segs)):
+        torch.testing.assert_close(sums[g, 0], part.sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
+        torch.testing.assert_close(sums[g, 1], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(m.weight.grad, wr.grad, rtol=5e-2, atol=5e-2 * wr.grad.abs().max().item())
+
+
+def test_bottleneck_with_gemm_convolutions_matches_library_path():
+    from tspipe_b200.batchnorm import DeferredBatchNorm
+    from tspipe_b200.models.resnet import Bottleneck
+    from tspipe_b200.ops import conv, gemm
+    torch.manual_seed(4)
+    dev = torch.device("cuda", 0)
+    blk = DeferredBatchNorm.convert_deferred_batch_norm(Bottleneck(256, 64), chunks=10 ** 9).to(dev)
+    blk = blk.to(memory_format=torch.channels_last)
+    x = torch.randn(8, 256, 16, 16, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    outs, grads = [], []
+    for flag in (False, True):
+        conv.set_conv1x1(flag)
+        conv.clear_weight_cache()
+        try:
+            xi = x.clone().requires_grad_()
+            blk.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = blk(xi)
+            y.float().square().mean().backward()
+        finally:
+            conv.set_conv1x1(False)
+        outs.append(y.float())
+        grads.append([xi.grad.float()] + [p.grad.clone() for p in blk.parameters()])
+    gemm.check_status()
+    torch.testing.assert_close(outs[1], outs[0], rtol=3e-2, atol=3e-2)
+    for a, b in zip(grads[1], grads[0]):
+        torch.testing.assert_close(a, b, rtol=5e-2, atol=5e-2 * max(b.abs().max().item(), 1e-3))

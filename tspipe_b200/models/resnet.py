@@ -15,6 +15,7 @@ import torch
 from torch import nn
 
 from ..ops.bn import bn_act
+from ..ops.conv import conv_bn_act
 from ..ops.pool import MaxPool3x3s2
 
 
@@ -34,9 +35,9 @@ class Bottleneck(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         identity = x if self.downsample is None else self.downsample(x)
-        out = bn_act(self.bn1, self.conv1(x), relu=True)
+        out = conv_bn_act(self.conv1, self.bn1, x, relu=True)
         out = bn_act(self.bn2, self.conv2(out), relu=True)
-        return bn_act(self.bn3, self.conv3(out), residual=identity, relu=True)
+        return conv_bn_act(self.conv3, self.bn3, out, residual=identity, relu=True)
 
 
 class BasicBlock(nn.Module):

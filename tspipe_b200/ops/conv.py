@@ -1,5 +1,6 @@
-"""ResNet stem convolution (7 x 7, stride 2, 3 -> 64 channels) on the tcgen05 kernel of
-``csrc/conv_stem_tcgen05.cu``, with the following BatchNorm's statistics computed in its epilogue.
+"""Convolutions with their own tcgen05 kernels, each with the following BatchNorm's statistics computed in the
+epilogue: the ResNet stem (7 x 7, stride 2, 3 -> 64 channels; ``csrc/conv_stem_tcgen05.cu``) and 1 x 1 stride-1
+convolutions of channels-last activations, which are plain GEMMs (``csrc/gemm_tcgen05_2cta.cu``, statistics variant).
 
 Reference call site: ``conv1`` of the torchvision ResNet that `benchmarks/byol/models/resnet_base_network.py`
 wraps (a library convolution there).  The weight gradient stays a library call
@@ -88,3 +89,93 @@ def stem_conv(x: torch.Tensor, weight: torch.Tensor, want_sums: bool = True, seg
         segments = 1
     y, sums = _StemConv.apply(x, weight, want_sums, segments)
     return y, (sums if want_sums else None)
+
+
+# -------------------------------------------------------------------------------------------------
+# 1 x 1 convolution = GEMM over the [N*H*W, Cin] view of a channels-last activation
+# -------------------------------------------------------------------------------------------------
+_CONV1X1 = False
+_W16 = {}        # id(weight) -> bf16 [Cout, Cin] copy; dropped at every optimizer step (clear_weight_cache)
+
+
+def set_conv1x1(flag: bool) -> None:
+    """Route eligible 1 x 1 convolutions that feed a training-mode BatchNorm through the tcgen05 GEMM."""
+    global _CONV1X1
+    _CONV1X1 = bool(flag)
+
+
+def clear_weight_cache() -> None:
+    _W16.clear()
+
+
+def _w16(weight: torch.Tensor) -> torch.Tensor:
+    w = _W16.get(id(weight))
+    if w is None or w.device != weight.device:
+        w = weight.detach().reshape(weight.shape[0], weight.shape[1]).to(torch.bfloat16).contiguous()
+        _W16[id(weight)] = w
+    return w
+
+
+def conv1x1_eligible(m: nn.Module, x: torch.Tensor, segments: int = 1) -> bool:
+    if not (isinstance(m, nn.Conv2d) and m.kernel_size == (1, 1) and m.stride == (1, 1) and m.padding == (0, 0)
+            and m.groups == 1 and m.bias is None):
+        return False
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16):
+        return False
+    n, c, h, w = x.shape
+    rows = n * h * w
+    if c % 8 or m.out_channels % 8 or c < 64 or rows % segments or (rows // segments) % 128:
+        return False
+    return x.stride() == (h * w * c, 1, w * c, c) and x.data_ptr() % 16 == 0
+
+
+class _Conv1x1(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, segs):
+        n, cin, h, w = x.shape
+        cout = weight.shape[0]
+        rows = n * h * w
+        w16 = _w16(weight)
+        y = torch.empty((n, cout, h, w), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
+        sums = torch.zeros(segs * 2 * cout, dtype=torch.float32, device=x.device)
+        L = _f.lib()
+        L.tsp_gemm_bf16_tn_2cta_stats.restype = _c.c_int
+        with torch.cuda.device(x.device):
+            code = L.tsp_gemm_bf16_tn_2cta_stats(_f._ptr(x), _f._ptr(w16), _f._ptr(y), _c.c_int(rows), _c.c_int(cout),
+                                                 _c.c_int(cin), _c.c_int(cin), _c.c_int(cin), _c.c_int(cout),
+                                                 _f._ptr(sums), _c.c_int(segs), _f._ptr(_gemm._status_word(x.device)),
+                                                 _f._stream())
+        _f._check(code, "tsp_gemm_bf16_tn_2cta_stats")
+        _f._count()
+        ctx.save_for_backward(x, weight)
+        ctx.mark_non_differentiable(sums)
+        return y, sums
+
+    @staticmethod
+    def backward(ctx, dy, _dsums):
+        x, weight = ctx.saved_tensors
+        w4 = _w16(weight).view(weight.shape[0], weight.shape[1], 1, 1)
+        gi, gw, _ = torch.ops.aten.convolution_backward(
+            dy.contiguous(memory_format=torch.channels_last), x, w4, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
+            [ctx.needs_input_grad[0], ctx.needs_input_grad[1], False])
+        return gi, (gw.to(weight.dtype) if gw is not None else None), None
+
+
+def conv1x1(x: torch.Tensor, weight: torch.Tensor, segments: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(y, sums)`` for a 1 x 1 stride-1 convolution of a channels-last bf16 activation: ``y`` bf16 channels-last,
+    ``sums`` = ``[segments][sum | sum of squares]`` per output channel (fp32) over each group of rows."""
+    return _Conv1x1.apply(x, weight, segments)
+
+
+def conv_bn_act(conv: nn.Module, bn: nn.Module, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                relu: bool = False) -> torch.Tensor:
+    """``relu(bn(conv(x)) + residual)``.  A 1 x 1 stride-1 convolution in front of a training-mode BatchNorm runs on
+    the tcgen05 GEMM whose epilogue already produces the BatchNorm's statistics (one pass over the activation
+    less); everything else is the library convolution followed by :func:`tspipe_b200.ops.bn.bn_act`."""
+    from . import bn as _bn
+    if _CONV1X1 and bn.training and torch.is_autocast_enabled():
+        segs = _bn.current_segments()
+        if conv1x1_eligible(conv, x, segs):
+            y, sums = conv1x1(x, conv.weight, segs)
+            return _bn.bn_act(bn, y, residual, relu, sums=sums if _bn.applicable(bn, y) else None)
+    return _bn.bn_act(bn, conv(x), residual, relu)

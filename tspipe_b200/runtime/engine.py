@@ -942,6 +942,9 @@ class StageEngine:
             self.flat_online.zero_grad()
             if self._amp_open:
                 torch.clear_autocast_cache()
+            if self.cuda:
+                from ..ops import conv as _conv
+                _conv.clear_weight_cache()          # bf16 weight copies of the tcgen05 convolutions
             self.steps_done += 1
 
     def _dp_sync(self) -> None:
