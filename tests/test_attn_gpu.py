@@ -34,24 +34,58 @@ def test_flash_forward_head_dim_64(b, h, nq, nk):
 
 
 def test_attention_dispatch_and_vit_block_without_grad():
+    """A ViT block gives the same result through the three attention paths: tcgen05 kernel (no gradient needed,
+    opt-in), the library's fused attention on unbound q / k / v, and the packed-qkv library entry point."""
     from tspipe_b200.models.vit import CONFIGS, Block
     from tspipe_b200.ops import attention, gemm
     torch.manual_seed(1)
     dev = torch.device("cuda", 0)
     blk = Block(CONFIGS["vit_base"]).to(dev)
     x = torch.randn(4, 197, 768, device=dev)
-    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-        y = blk(x)                                   # tcgen05 attention (no gradient needed)
-        attention.set_tcgen05(False)
-        try:
-            y_ref = blk(x)                           # library attention
-        finally:
+    try:
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            attention.set_packed(False)
             attention.set_tcgen05(True)
+            y = blk(x)                                   # tcgen05 attention
+            attention.set_tcgen05(False)
+            y_ref = blk(x)                               # library attention on unbound q, k, v
+            attention.set_packed(None)
+            y_packed = blk(x)                            # packed entry point when the library supports this GPU
+    finally:
+        attention.set_tcgen05(False)
+        attention.set_packed(None)
     gemm.check_status()
     torch.testing.assert_close(y.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(y_packed.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
+    xg = x.clone().requires_grad_()
     with torch.autocast("cuda", dtype=torch.bfloat16):
-        blk(x.requires_grad_()).float().sum().backward()    # with gradients: library path, must still work
-    assert x.grad is not None
+        blk(xg).float().sum().backward()                 # with gradients
+    g_packed = xg.grad.clone()
+    attention.set_packed(False)
+    try:
+        xg2 = x.clone().requires_grad_()
+        blk.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            blk(xg2).float().sum().backward()
+    finally:
+        attention.set_packed(None)
+    torch.testing.assert_close(g_packed, xg2.grad, rtol=5e-2, atol=5e-2 * xg2.grad.abs().max().item())
+
+
+def test_patch_embedding_as_gemm_matches_convolution():
+    from tspipe_b200.models.vit import CONFIGS, PatchEmbed
+    torch.manual_seed(5)
+    dev = torch.device("cuda", 0)
+    pe = PatchEmbed(CONFIGS["vit_base"]).to(dev)
+    for fmt in (torch.contiguous_format, torch.channels_last):
+        x = torch.randn(3, 3, 224, 224, device=dev).contiguous(memory_format=fmt).requires_grad_()
+        y = pe(x)
+        ref = pe.proj(x).flatten(2).transpose(1, 2)
+        torch.testing.assert_close(y, ref, rtol=2e-3, atol=2e-3)     # TF32 may be on for either path
+        g = torch.randn_like(y)
+        gw = torch.autograd.grad(y, pe.proj.weight, g, retain_graph=True)[0]
+        gw_ref = torch.autograd.grad(ref, pe.proj.weight, g)[0]
+        torch.testing.assert_close(gw, gw_ref, rtol=2e-3, atol=2e-3 * gw_ref.abs().max().item())
 
 
 @pytest.mark.parametrize("n", [128, 1024, 4096])

@@ -18,12 +18,48 @@ from typing import Optional, Tuple
 import torch
 import torch.nn.functional as F
 
-_TCGEN05 = True
+# The tcgen05 kernel launches one CTA per (128-query tile, head): at ViT sizes (197 tokens) that is two key tiles per
+# CTA and the per-CTA start-up dominates (343 us against the library's 105 us on [256, 12, 197, 64]), so it is opt-in
+# for attention; the contrastive loss (long key loops) uses it by default.
+_TCGEN05 = False
 
 
 def set_tcgen05(flag: bool) -> None:
     global _TCGEN05
     _TCGEN05 = bool(flag)
+
+
+_PACKED = {"state": None}     # None = not probed yet, True / False = usable or not
+
+
+def set_packed(flag: Optional[bool]) -> None:
+    """Force (True / False) or re-probe (None) the packed-qkv library attention."""
+    _PACKED["state"] = flag
+
+
+def packed_attention(qkv: torch.Tensor) -> Optional[torch.Tensor]:
+    """Attention on the packed projection output ``qkv [B, N, 3, H, D]`` -> ``[B, N, H, D]`` through the
+    flash-attn library's packed entry point, or None when that is not usable here.  Compared with unbinding q, k, v
+    for the generic fused attention this avoids two full-size copies per block and step: the concatenation of
+    dq, dk, dv that autograd builds for the packed tensor, and the ``[B, H, N, D] -> [B, N, H * D]`` repacking of
+    the output."""
+    if _PACKED["state"] is False or not (qkv.is_cuda and qkv.dtype in (torch.bfloat16, torch.float16)):
+        return None
+    if qkv.shape[-1] > 256 or qkv.shape[-1] % 8:
+        return None
+    try:
+        from flash_attn import flash_attn_qkvpacked_func
+        if _PACKED["state"] is None:
+            probe = torch.randn(1, 16, 3, 1, 64, device=qkv.device, dtype=torch.bfloat16)
+            ref = F.scaled_dot_product_attention(*(t.transpose(1, 2) for t in probe.unbind(2))).transpose(1, 2)
+            ok = torch.allclose(flash_attn_qkvpacked_func(probe).float(), ref.float(), rtol=3e-2, atol=3e-2)
+            _PACKED["state"] = bool(ok)
+            if not ok:
+                return None
+        return flash_attn_qkvpacked_func(qkv)
+    except Exception:   # noqa: BLE001 - library missing or not built for this GPU: use the generic path
+        _PACKED["state"] = False
+        return None
 
 
 def _strides3(t: torch.Tensor):
