@@ -35,6 +35,7 @@ constexpr int kAStageBytes = 3 * kABlockBytes;
 constexpr int kBBlockBytes = kCout * 128;
 constexpr int kBBytes = 3 * kBBlockBytes;
 constexpr int kRingSlots = 16;
+constexpr int kAhead = 3;                 // output rows between the fetch of an input row pair and its use (7 + 2 * kAhead <= 16)
 constexpr int kRowElems = 704;            // 16 leading pad + up to 672 data + trailing zeros
 constexpr int kRowBytes = kRowElems * 2;
 constexpr int kRingBytes = kRingSlots * kRowBytes;
@@ -211,19 +212,30 @@ conv_stem_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
     for (int t = t_begin; t < t_end && ok; ++t, ++it) {
       const int n = t / oh_n, oh = t - n * oh_n;
       const int ih0 = 2 * oh - 3;
-      if (n != have_n || oh != have_oh + 1) {
-        producer_barrier();                        // nobody still reads rows of the previous tile
+      // Input rows are fetched kAhead output rows ahead of their use (global latency is a few tile times): at
+      // tile t the copies of tile t + kAhead are issued and all but the kAhead - 1 most recent groups are awaited.
+      if (n != have_n || oh != have_oh + 1) {      // start of a run of consecutive output rows of one image
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        producer_barrier();                        // nobody still reads rows of the previous run
         ring_load(ring, x, n, ih0, ih0 + 6, h, w, tid);
+#pragma unroll
+        for (int d = 1; d < kAhead; ++d) {
+          if (t + d < t_end && oh + d < oh_n) ring_load(ring, x, n, ih0 + 5 + 2 * d, ih0 + 6 + 2 * d, h, w, tid);
+          else asm volatile("cp.async.commit_group;" ::: "memory");
+        }
       }
       const int s = it % kAStages;
       const uint32_t round = it / kAStages;
       bool mine = true;
       if (round > 0) mine = mbar_wait(empty_bar + s, (round - 1) & 1, status, 1);
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");
       ok = producer_barrier_and(mine);             // this tile's rows are in the ring, for every thread
       if (!ok) break;
       have_n = n; have_oh = oh;
-      if (t + 1 < t_end && oh + 1 < oh_n) ring_load(ring, x, n, ih0 + 7, ih0 + 8, h, w, tid);   // next tile's new rows
+      if (t + kAhead < t_end && oh + kAhead < oh_n)
+        ring_load(ring, x, n, ih0 + 5 + 2 * kAhead, ih0 + 6 + 2 * kAhead, h, w, tid);
+      else
+        asm volatile("cp.async.commit_group;" ::: "memory");
       if (p < ow_n) {
         uint8_t* a_stage = a_tiles + s * kAStageBytes;
         const uint32_t row_off = (uint32_t)(p >> 3) * 1024u + (uint32_t)(p & 7) * 128u;

@@ -146,11 +146,11 @@ struct BMaps {
 // Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...  Two accumulator
 // buffers in TMEM let the epilogue of tile i run while the MMAs of tile i+1 are issued; the smem ring keeps
 // streaming across tile boundaries.
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ BMaps bmaps,
                     const __grid_constant__ CUtensorMap tmap_c, int tma_store, int rows_per_b, OutT* __restrict__ c, const float* __restrict__ bias, int m, int n, int k, int ldc,
-                    int epi, int* __restrict__ status) {
+                    int epi, float* __restrict__ col_sums, int seg_rows, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   using C = Cfg<BN>;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -258,16 +258,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint8_t* my_bufs = store_bufs + quarter * 2 * kStoreBufBytes;
     uint32_t lt = 0, nstore = 0;
     bool ok = true;
+    // STATS: per-column sum and sum of squares of the rounded outputs (the statistics of a BatchNorm that
+    // follows a 1x1 convolution), kept in registers while this warp stays in the same column block and row
+    // group: cs[i] = {sum, sumsq of column 2*lane, sum, sumsq of column 2*lane+1} of 64-column block i.
+    constexpr int kStatBlocks = BN / 64;
+    float cs[kStatBlocks][4];
+#pragma unroll
+    for (int i = 0; i < kStatBlocks; ++i) { cs[i][0] = cs[i][1] = cs[i][2] = cs[i][3] = 0.f; }
+    int cur_n0 = -1, cur_seg = 0;
+    auto flush_stats = [&]() {
+      if (cur_n0 >= 0) {
+        float* dst = col_sums + (int64_t)cur_seg * 2 * n;
+#pragma unroll
+        for (int i = 0; i < kStatBlocks; ++i) {
+          const int col = cur_n0 + 64 * i + 2 * lane;
+          if (col < n) { atomicAdd(dst + col, cs[i][0]); atomicAdd(dst + n + col, cs[i][1]); }
+          if (col + 1 < n) { atomicAdd(dst + col + 1, cs[i][2]); atomicAdd(dst + n + col + 1, cs[i][3]); }
+          cs[i][0] = cs[i][1] = cs[i][2] = cs[i][3] = 0.f;
+        }
+      }
+    };
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
       const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
       const uint32_t acc = lt & 1, use = lt >> 1;
+      if (STATS) {
+        const int seg = m0 / seg_rows;
+        if (n0 != cur_n0 || seg != cur_seg) { flush_stats(); cur_n0 = n0; cur_seg = seg; }
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3));   // one way out per warp
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row0 = m0 + quarter * 32, row = row0 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += kCols) {
-        if (n0 + c0 >= n) break;                  // columns past the matrix edge: nothing to convert or store
+      // one block of kCols columns; returns false past the matrix edge
+      auto chunk = [&](int c0, float* st) -> bool {
+        if (n0 + c0 >= n) return false;            // columns past the matrix edge: nothing to convert or store
         float v[kCols];
         {
           uint32_t r[kCols];
@@ -316,18 +340,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             else asm volatile("cp.async.bulk.commit_group;" ::: "memory");     // keep the group count in step
           }
           ++nstore;
+          if (STATS && st != nullptr) {
+            // column sums of the staged (rounded) block: lane owns columns 2*lane, 2*lane+1; rows past the
+            // matrix edge hold exact zeros (their A rows were zero-filled)
+#pragma unroll 8
+            for (int rr = 0; rr < 32; ++rr) {
+              const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                                     (lane & 3) * 4);
+              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
+              st[0] += f.x; st[1] += f.x * f.x; st[2] += f.y; st[3] += f.y * f.y;
+            }
+          }
         } else if (row < m && col < n) {
           OutT* dst = c + (int64_t)row * ldc + col;
 #pragma unroll
           for (int j = 0; j < kCols; ++j)       // constant indices only: v stays in registers
             if (col + j < n) tsp::st(dst, j, v[j]);
         }
+        return true;
+      };
+      if constexpr (STATS) {
+        static_assert(!STATS || kCols == 64, "column statistics are kept for bf16 outputs");
+        bool more = true;
+#pragma unroll
+        for (int i = 0; i < kStatBlocks; ++i)
+          if (more) more = chunk(64 * i, cs[i]);
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kCols)
+          if (!chunk(c0, nullptr)) break;
       }
       // this warp has drained its quarter of the accumulator: hand the buffer back to the MMA issuer
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar + acc);
     }
+    if (STATS) flush_stats();
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staging buffers are free again
     __syncwarp();
   }
@@ -384,9 +432,10 @@ bool make_store_map(CUtensorMap* map, void* ptr, int rows, int cols, int ld, boo
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool STATS = false>
 int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* c, const float* bias, int m, int n,
-           int k, int lda, int ldb, int ldc, int epi, int* status, cudaStream_t stream) {
+           int k, int lda, int ldb, int ldc, int epi, int* status, cudaStream_t stream, float* col_sums = nullptr,
+           int seg_rows = 1) {
   CUtensorMap ta;
   BMaps tb;
   if (!make_map(&ta, a, m, k, lda, BM)) return -6;
@@ -398,7 +447,8 @@ int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* 
   CUtensorMap tc = ta;          // placeholder when C cannot be described (the kernel then stores directly)
   const bool aligned_c = (((uintptr_t)c & 15) == 0) && ((ldc * (int)sizeof(OutT)) % 16 == 0);
   const int tma_store = aligned_c && make_store_map(&tc, c, m, n, ldc, sizeof(OutT) == 2) ? 1 : 0;
-  auto kern = gemm_tcgen05_kernel<BN, OutT>;
+  if (STATS && !tma_store) return -3;           // the statistics are taken from the staged blocks
+  auto kern = gemm_tcgen05_kernel<BN, OutT, STATS>;
   static bool attr_set[64] = {};
   static int n_sm[64] = {};
   int dev = 0;
@@ -414,7 +464,7 @@ int launch(const void* a, void* const* b_srcs, int n_src, int rows_per_b, void* 
   const int num_tiles = ((n + BN - 1) / BN) * ((m + BM - 1) / BM);
   const int grid = num_tiles < n_sm[dev] ? num_tiles : n_sm[dev];
   kern<<<grid, kThreads, Cfg<BN>::kSmemBytes, stream>>>(ta, tb, tc, tma_store, n_src == 1 ? n + BN : rows_per_b,
-                                                        (OutT*)c, bias, m, n, k, ldc, epi, status);
+                                                        (OutT*)c, bias, m, n, k, ldc, epi, col_sums, seg_rows, status);
   return TSP_LAUNCH_CHECK();
 }
 
@@ -462,6 +512,23 @@ int tsp_gemm_bf16_tn_gathered_b(const void* a, void* const* b_srcs, int n_src, i
                 : launch<128, __nv_bfloat16>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream);
   return wide ? launch<256, float>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream)
               : launch<128, float>(a, b_srcs, n_src, rows_per_b, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream);
+}
+
+// C (bf16) = A B^T plus per-column statistics of the rounded result for a BatchNorm that follows: col_sums
+// [segs][2n] fp32 (zeroed by the caller) receives, for each of the `segs` consecutive groups of m / segs rows, the
+// column sums and the column sums of squares.  m / segs must be a multiple of 128; C 16-byte aligned with a row
+// pitch that is a multiple of 16 bytes.
+int tsp_gemm_bf16_tn_stats(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
+                           float* col_sums, int segs, int* status, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (k % 8) || segs < 1 || m % segs != 0 || (m / segs) % 128 != 0) return -3;
+  if (((uintptr_t)a | (uintptr_t)b) & 15) return -2;
+  void* const srcs[1] = {const_cast<void*>(b)};
+  if (n > 128)
+    return launch<256, __nv_bfloat16, true>(a, srcs, 1, n, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream, col_sums,
+                                            m / segs);
+  return launch<128, __nv_bfloat16, true>(a, srcs, 1, n, c, nullptr, m, n, k, lda, ldb, ldc, 0, status, stream, col_sums,
+                                          m / segs);
 }
 
 }  // extern "C"

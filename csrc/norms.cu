@@ -245,17 +245,36 @@ __global__ void __launch_bounds__(256) ln_bwd_reduce_kernel(const float* __restr
 // ---------------------------------------------------------------------------------------------
 // GELU (erf form), optionally with the bias add in front: y = gelu(x + bias)
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// erf through the rational form of Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7, below fp32 resolution of the
+// products it enters): one reciprocal, one exponential and six FMAs instead of the two-branch library routine -
+// these kernels are bound by instruction issue, not by memory.  E = exp(-z^2) is returned for the backward.
+__device__ __forceinline__ float erf_fast(float z, float& e_out) {
+  const float az = fabsf(z);
+  const float t = __frcp_rn(fmaf(0.3275911f, az, 1.f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  p *= t;
+  const float e = exp2f(-1.4426950408889634f * az * az);
+  e_out = e;
+  return copysignf(fmaf(-p, e, 1.f), z);
+}
+__device__ __forceinline__ float gelu_f(float x) {
+  float e;
+  return 0.5f * x * (1.f + erf_fast(x * 0.70710678118654752f, e));
+}
 __device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float e;                                        // e = exp(-x^2 / 2): the Gaussian density needs it too
+  const float cdf = 0.5f * (1.f + erf_fast(x * 0.70710678118654752f, e));
+  return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ x, const float* __restrict__ bias,
                                                        T* __restrict__ y, int64_t n, int d) {
   const int64_t nv = n >> 3;
+#pragma unroll 2
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (int64_t)gridDim.x * blockDim.x) {
     float v[8], o[8];
     tsp::ld8(x, i * 8, v);

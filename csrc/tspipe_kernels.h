@@ -97,6 +97,9 @@ int tsp_attn_nce_gathered(const void* q, void* const* k_srcs, int n_src, int row
 int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int n, int h, int w, int segs,
                       int* status, cudaStream_t stream);
 
+int tsp_gemm_bf16_tn_stats(const void* a, const void* b, void* c, int m, int n, int k, int lda, int ldb, int ldc,
+                           float* col_sums, int segs, int* status, cudaStream_t stream);
+
 // ---- gemm_tcgen05_2cta.cu -----------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn_2cta(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda,
                           int ldb, int ldc, int out_dtype, int epi, int* status, cudaStream_t stream);

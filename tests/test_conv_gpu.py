@@ -83,16 +83,25 @@ def test_stem_conv_statistics_per_group_of_images():
 
 @pytest.mark.parametrize("shape,cout,segs", [((4, 64, 16, 16), 256, 1), ((8, 256, 8, 8), 64, 2), ((2, 512, 16, 8), 1024, 2),
                                              ((6, 128, 16, 16), 520, 1)])
-def test_conv1x1_gemm_with_batchnorm_statistics(shape, cout, segs):
+@pytest.mark.parametrize("pair", [False, True])
+def test_conv1x1_gemm_with_batchnorm_statistics(shape, cout, segs, pair):
     """1 x 1 convolution on the tcgen05 GEMM: output, per-group column statistics and gradients vs F.conv2d."""
     from tspipe_b200.ops import conv, gemm
     torch.manual_seed(3)
     dev = torch.device("cuda", 0)
     x = torch.randn(shape, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last).requires_grad_()
     m = nn.Conv2d(shape[1], cout, 1, bias=False).to(dev)
-    assert conv.conv1x1_eligible(m, x, segs)
+    conv._MIN_COUT = 64
+    try:
+        assert conv.conv1x1_eligible(m, x, segs)
+    finally:
+        conv._MIN_COUT = 256
     conv.clear_weight_cache()
-    y, sums = conv.conv1x1(x, m.weight, segs)
+    conv._PAIR = pair
+    try:
+        y, sums = conv.conv1x1(x, m.weight, segs)
+    finally:
+        conv._PAIR = False
     gemm.check_status()
     xr = x.detach().float().requires_grad_()
     wr = m.weight.detach().bfloat16().float().requires_grad_()
@@ -116,7 +125,7 @@ def test_bottleneck_with_gemm_convolutions_matches_library_path():
     from tspipe_b200.ops import conv, gemm
     torch.manual_seed(4)
     dev = torch.device("cuda", 0)
-    blk = DeferredBatchNorm.convert_deferred_batch_norm(Bottleneck(256, 64), chunks=10 ** 9).to(dev)
+    blk = DeferredBatchNorm.convert_deferred_batch_norm(Bottleneck(256, 64), chunks=10 ** 9).to(dev)   # conv3: 64 -> 256
     blk = blk.to(memory_format=torch.channels_last)
     x = torch.randn(8, 256, 16, 16, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
     outs, grads = [], []

@@ -95,6 +95,8 @@ def stem_conv(x: torch.Tensor, weight: torch.Tensor, want_sums: bool = True, seg
 # 1 x 1 convolution = GEMM over the [N*H*W, Cin] view of a channels-last activation
 # -------------------------------------------------------------------------------------------------
 _CONV1X1 = False
+_PAIR = False        # CTA-pair kernel instead of one CTA per tile (the latter is faster on tall, narrow products)
+_MIN_COUT = 256      # narrower outputs: the library convolution plus a statistics pass is as fast or faster
 _W16 = {}        # id(weight) -> bf16 [Cout, Cin] copy; dropped at every optimizer step (clear_weight_cache)
 
 
@@ -124,7 +126,8 @@ def conv1x1_eligible(m: nn.Module, x: torch.Tensor, segments: int = 1) -> bool:
         return False
     n, c, h, w = x.shape
     rows = n * h * w
-    if c % 8 or m.out_channels % 8 or c < 64 or rows % segments or (rows // segments) % 128:
+    if c % 8 or m.out_channels % 8 or c < 64 or m.out_channels < _MIN_COUT or rows % segments \
+            or (rows // segments) % 128:
         return False
     return x.stride() == (h * w * c, 1, w * c, c) and x.data_ptr() % 16 == 0
 
@@ -139,13 +142,14 @@ class _Conv1x1(torch.autograd.Function):
         y = torch.empty((n, cout, h, w), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         sums = torch.zeros(segs * 2 * cout, dtype=torch.float32, device=x.device)
         L = _f.lib()
-        L.tsp_gemm_bf16_tn_2cta_stats.restype = _c.c_int
+        fn = L.tsp_gemm_bf16_tn_2cta_stats if _PAIR else L.tsp_gemm_bf16_tn_stats
+        fn.restype = _c.c_int
         with torch.cuda.device(x.device):
-            code = L.tsp_gemm_bf16_tn_2cta_stats(_f._ptr(x), _f._ptr(w16), _f._ptr(y), _c.c_int(rows), _c.c_int(cout),
+            code = fn(_f._ptr(x), _f._ptr(w16), _f._ptr(y), _c.c_int(rows), _c.c_int(cout),
                                                  _c.c_int(cin), _c.c_int(cin), _c.c_int(cin), _c.c_int(cout),
                                                  _f._ptr(sums), _c.c_int(segs), _f._ptr(_gemm._status_word(x.device)),
                                                  _f._stream())
-        _f._check(code, "tsp_gemm_bf16_tn_2cta_stats")
+        _f._check(code, "tsp_gemm_bf16_tn_stats")
         _f._count()
         ctx.save_for_backward(x, weight)
         ctx.mark_non_differentiable(sums)
