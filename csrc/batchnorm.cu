@@ -187,7 +187,8 @@ __device__ __forceinline__ bool stream_wait(uint64_t* bar, uint32_t parity, int 
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    if (*((volatile int*)&g_bn_status) != 0) return false;
+    // the error word lives in global memory: look at it only now and then
+    if ((spin & 255u) == 255u && *((volatile int*)&g_bn_status) != 0) return false;
   }
   atomicCAS(&g_bn_status, 0, code);
   return false;

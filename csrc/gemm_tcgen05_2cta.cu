@@ -75,7 +75,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    if (*((volatile int*)status) != 0) return false;
+    // the error word lives in global memory: look at it only now and then, or every poll of the barrier
+    // would cost a round trip to L2
+    if ((spin & 255u) == 255u && *((volatile int*)status) != 0) return false;
   }
   atomicCAS(status, 0, code);
   return false;
