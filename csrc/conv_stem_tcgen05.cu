@@ -67,9 +67,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    // the error word lives in global memory: look at it only now and then, or every poll of the barrier
-    // would cost a round trip to L2
-    if ((spin & 255u) == 255u && *((volatile int*)status) != 0) return false;
+    // The error word lives in global memory, so this check costs a round trip to L2 per failed poll.  That is
+    // deliberate: it is the back-off of the spin loop.  Polling the barrier flat out was measured slower (the
+    // waiting warps take issue slots from the one thread that feeds the pipeline).
+    if (*((volatile int*)status) != 0) return false;
   }
   atomicCAS(status, 0, code);
   return false;

