@@ -270,12 +270,19 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
+// Column (in 8-element vectors) of vector i in a matrix with cpv vectors per row.  A 64-bit remainder by a run-time
+// value costs about a hundred instructions; vector counts fit 32 bits in practice.
+__device__ __forceinline__ uint32_t bias_col(int64_t i, uint32_t cpv) {
+  return i < (int64_t)0xffffffffu ? (uint32_t)i % cpv : (uint32_t)(i % (int64_t)cpv);
+}
+
 // Four independent 8-element vectors per thread and trip: all loads are issued before the first use (a single
 // load in flight per thread left these kernels at 3 TB/s).
 template <typename T>
 __global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ x, const float* __restrict__ bias,
                                                        T* __restrict__ y, int64_t n, int d) {
   const int64_t nv = n >> 3;
+  const uint32_t cpv = (uint32_t)(d >> 3);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + 3 * stride < nv; i += 4 * stride) {
@@ -288,7 +295,7 @@ __global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ x, 
       tsp::cvt8(raw[u], v);
       if (bias) {
         float b[8];
-        tsp::ld8(bias, ((i + u * stride) * 8) % d, b);
+        tsp::ld8(bias, (int64_t)bias_col(i + u * stride, cpv) * 8, b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] += b[e];
       }
@@ -302,7 +309,7 @@ __global__ void __launch_bounds__(256) gelu_fwd_kernel(const T* __restrict__ x, 
     tsp::ld8(x, i * 8, v);
     if (bias) {
       float b[8];
-      tsp::ld8(bias, (i * 8) % d, b);
+      tsp::ld8(bias, (int64_t)bias_col(i, cpv) * 8, b);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += b[e];
     }
@@ -317,6 +324,7 @@ __global__ void __launch_bounds__(256) gelu_bwd_kernel(const T* __restrict__ dy,
                                                        const float* __restrict__ bias, T* __restrict__ dx, int64_t n,
                                                        int d) {
   const int64_t nv = n >> 3;
+  const uint32_t cpv = (uint32_t)(d >> 3);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   for (; i + stride < nv; i += 2 * stride) {
@@ -330,7 +338,7 @@ __global__ void __launch_bounds__(256) gelu_bwd_kernel(const T* __restrict__ dy,
       tsp::cvt8(gr[u], g);
       if (bias) {
         float b[8];
-        tsp::ld8(bias, ((i + u * stride) * 8) % d, b);
+        tsp::ld8(bias, (int64_t)bias_col(i + u * stride, cpv) * 8, b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] += b[e];
       }
@@ -345,7 +353,7 @@ __global__ void __launch_bounds__(256) gelu_bwd_kernel(const T* __restrict__ dy,
     tsp::ld8(dy, i * 8, g);
     if (bias) {
       float b[8];
-      tsp::ld8(bias, (i * 8) % d, b);
+      tsp::ld8(bias, (int64_t)bias_col(i, cpv) * 8, b);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += b[e];
     }
