@@ -16,7 +16,6 @@ import os
 import sys
 import time
 from argparse import Namespace
-from collections import OrderedDict
 
 import torch
 from torch import nn

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import pickle
 from collections import deque
-from typing import Any, Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Deque, Dict, List, Sequence, Tuple
 
 import torch
 import torch.distributed as dist

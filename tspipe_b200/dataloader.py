@@ -9,8 +9,7 @@ throughput-only runs.
 """
 from __future__ import annotations
 
-import multiprocessing as pymp
-from typing import Any, Iterator, Optional, Sequence, Tuple
+from typing import Any, Iterator
 
 import torch
 from torch.utils.data import DataLoader

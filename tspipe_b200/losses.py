@@ -12,7 +12,7 @@ On CUDA with ``runtime.fused`` these dispatch to the sm_100a kernels in
 """
 from __future__ import annotations
 
-from typing import Any, List, Optional
+from typing import List
 
 import torch
 import torch.nn.functional as F

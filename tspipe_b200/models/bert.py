@@ -15,10 +15,9 @@ LayerNorm / bias+GELU are the fused kernels.
 """
 from __future__ import annotations
 
-import copy
 from collections import OrderedDict
 from dataclasses import dataclass
-from typing import Dict, Optional, Tuple
+from typing import Dict, Tuple
 
 import torch
 from torch import nn

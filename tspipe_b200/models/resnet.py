@@ -9,7 +9,7 @@ connection stays inside one stage), global pool, reshape, then the four head lay
 from __future__ import annotations
 
 from collections import OrderedDict
-from typing import List, Optional, Sequence
+from typing import Optional
 
 import torch
 from torch import nn

@@ -7,7 +7,7 @@ library cannot be loaded on a CUDA machine.
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 

@@ -12,8 +12,7 @@ Semantics (reference: `tspipe/gpu_task.py:58-66` version rule, `:89-226` full-ba
 """
 from __future__ import annotations
 
-import copy
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Callable, Dict, List, Optional
 
 import torch
 from torch import nn

@@ -14,7 +14,6 @@ funnelling rows to rank 0 over RPC (`tspipe/profiler.py:95-114`).
 """
 from __future__ import annotations
 
-import contextlib
 import csv
 import os
 import queue

@@ -16,7 +16,7 @@ teacher stage the plan lists contiguous runs of the flat buffers:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 from torch import nn
 

@@ -34,7 +34,7 @@ from ..comm.links import Link, MetaBoard
 from ..comm.peer import PeerView
 from ..logger import Log
 from ..utils import pytree as pt
-from .engine import EngineError, EpochMsg, FeedMsg, FlushMsg, StopMsg, _rebuild
+from .engine import EngineError, FeedMsg, FlushMsg, StopMsg, _rebuild
 from .state import FlatParams
 
 

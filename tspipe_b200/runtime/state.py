@@ -13,7 +13,7 @@ The schedule orders every teacher forward of batch ``b+1`` between ``OPT(b-1)`` 
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 from torch import nn

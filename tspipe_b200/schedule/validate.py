@@ -5,7 +5,7 @@ objects hashed by identity).  These checks are on values.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 from .generator import Op, OpKind, ScheduleSpec, device_program, simulate
 
