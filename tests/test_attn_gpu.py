@@ -51,12 +51,16 @@ def test_attention_dispatch_and_vit_block_without_grad():
             y_ref = blk(x)                               # library attention on unbound q, k, v
             attention.set_packed(None)
             y_packed = blk(x)                            # packed entry point when the library supports this GPU
+            attention.set_qkv_mode("split")
+            y_split = blk(x)                             # three projection GEMMs + library attention
     finally:
         attention.set_tcgen05(False)
         attention.set_packed(None)
+        attention.set_qkv_mode("packed")
     gemm.check_status()
     torch.testing.assert_close(y.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(y_packed.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(y_split.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
     xg = x.clone().requires_grad_()
     with torch.autocast("cuda", dtype=torch.bfloat16):
         blk(xg).float().sum().backward()                 # with gradients

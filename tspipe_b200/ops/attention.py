@@ -31,6 +31,21 @@ def set_tcgen05(flag: bool) -> None:
 
 _PACKED = {"state": None}     # None = not probed yet, True / False = usable or not
 
+# How the ViT blocks form q, k, v: "packed" = one projection GEMM and the packed-qkv library attention; "split" =
+# three projection GEMMs on slices of the weight and the generic fused attention (no packed tensor, hence no
+# concatenation of dq, dk, dv in the backward either).
+_QKV_MODE = "packed"
+
+
+def set_qkv_mode(mode: str) -> None:
+    global _QKV_MODE
+    assert mode in ("packed", "split")
+    _QKV_MODE = mode
+
+
+def qkv_mode() -> str:
+    return _QKV_MODE
+
 
 def set_packed(flag: Optional[bool]) -> None:
     """Force (True / False) or re-probe (None) the packed-qkv library attention."""
