@@ -44,6 +44,7 @@ def test_attention_dispatch_and_vit_block_without_grad():
     x = torch.randn(4, 197, 768, device=dev)
     try:
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            attention.set_qkv_mode("packed")
             attention.set_packed(False)
             attention.set_tcgen05(True)
             y = blk(x)                                   # tcgen05 attention
@@ -56,24 +57,24 @@ def test_attention_dispatch_and_vit_block_without_grad():
     finally:
         attention.set_tcgen05(False)
         attention.set_packed(None)
-        attention.set_qkv_mode("packed")
+        attention.set_qkv_mode("split")
     gemm.check_status()
     torch.testing.assert_close(y.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(y_packed.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
     torch.testing.assert_close(y_split.float(), y_ref.float(), rtol=3e-2, atol=3e-2)
-    xg = x.clone().requires_grad_()
-    with torch.autocast("cuda", dtype=torch.bfloat16):
-        blk(xg).float().sum().backward()                 # with gradients
-    g_packed = xg.grad.clone()
-    attention.set_packed(False)
-    try:
-        xg2 = x.clone().requires_grad_()
-        blk.zero_grad()
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            blk(xg2).float().sum().backward()
-    finally:
-        attention.set_packed(None)
-    torch.testing.assert_close(g_packed, xg2.grad, rtol=5e-2, atol=5e-2 * xg2.grad.abs().max().item())
+    grads = {}
+    for mode in ("split", "packed"):                      # with gradients, both ways of forming q, k, v
+        attention.set_qkv_mode(mode)
+        try:
+            xg = x.clone().requires_grad_()
+            blk.zero_grad()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                blk(xg).float().sum().backward()
+            grads[mode] = (xg.grad.clone(), blk.attn.qkv.weight.grad.clone())
+        finally:
+            attention.set_qkv_mode("split")
+    for a, b in zip(grads["split"], grads["packed"]):
+        torch.testing.assert_close(a, b, rtol=5e-2, atol=5e-2 * b.abs().max().item())
 
 
 def test_patch_embedding_as_gemm_matches_convolution():

@@ -34,7 +34,7 @@ _PACKED = {"state": None}     # None = not probed yet, True / False = usable or 
 # How the ViT blocks form q, k, v: "packed" = one projection GEMM and the packed-qkv library attention; "split" =
 # three projection GEMMs on slices of the weight and the generic fused attention (no packed tensor, hence no
 # concatenation of dq, dk, dv in the backward either).
-_QKV_MODE = "packed"
+_QKV_MODE = "split"      # measured on MoCo-v3 ViT-B, 256 samples per GPU: 114.8 ms per step against 121.3 ms for "packed"
 
 
 def set_qkv_mode(mode: str) -> None:
