@@ -24,7 +24,7 @@ from torch import nn
 
 from ..model_wrapper import TSPipeModelWrapper
 from ..ops import fused
-from ..ops.attention import attention
+from ..ops.attention import attention, project_qkv
 from ..ops.linear import linear
 from .vit import LayerNorm
 
@@ -86,8 +86,7 @@ class EncoderLayer(nn.Module):
     def forward(self, s: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
         x, mask = s["hidden"], s["mask"]
         b, l, c = x.shape
-        qkv = linear(x, self.qkv.weight, self.qkv.bias).reshape(b, l, 3, self.heads, c // self.heads)
-        q, k, v = qkv.permute(2, 0, 3, 1, 4)
+        q, k, v = project_qkv(x, self.qkv.weight, self.qkv.bias, self.heads)
         key_mask = mask.to(torch.bool)[:, None, None, :]
         a = attention(q, k, v, key_mask).transpose(1, 2).reshape(b, l, c)
         x = self.norm1(x + self.drop(linear(a, self.out.weight, self.out.bias)))

@@ -26,7 +26,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from ..ops import fused
-from ..ops.attention import attention, packed_attention, qkv_mode
+from ..ops.attention import attention, packed_attention, project_qkv, qkv_mode
 from ..ops.linear import linear
 
 
@@ -131,9 +131,7 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         b, n, c = x.shape
         if mask is None and x.is_cuda and qkv_mode() == "split":
-            w, bias = self.qkv.weight, self.qkv.bias
-            q, k, v = (linear(x, w[i * c:(i + 1) * c], bias[i * c:(i + 1) * c]).view(b, n, self.heads, c // self.heads)
-                       .transpose(1, 2) for i in range(3))
+            q, k, v = project_qkv(x, self.qkv.weight, self.qkv.bias, self.heads)
             o = attention(q, k, v).transpose(1, 2)
             return linear(o.reshape(b, n, c), self.proj.weight, self.proj.bias)
         qkv = linear(x, self.qkv.weight, self.qkv.bias).reshape(b, n, 3, self.heads, c // self.heads)

@@ -47,6 +47,19 @@ def qkv_mode() -> str:
     return _QKV_MODE
 
 
+def project_qkv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], heads: int):
+    """``q, k, v`` as ``[B, H, N, D]`` views from the fused projection parameters ``weight [3C, C]``, ``bias [3C]``.
+    On CUDA in "split" mode this is three GEMMs on slices of the parameters, so that no packed qkv tensor exists
+    whose gradient autograd would have to assemble from dq, dk and dv; otherwise one GEMM and an unbind."""
+    from .linear import linear
+    b, n, c = x.shape
+    if x.is_cuda and _QKV_MODE == "split":
+        return tuple(linear(x, weight[i * c:(i + 1) * c], None if bias is None else bias[i * c:(i + 1) * c])
+                     .view(b, n, heads, c // heads).transpose(1, 2) for i in range(3))
+    qkv = linear(x, weight, bias).reshape(b, n, 3, heads, c // heads)
+    return tuple(qkv.permute(2, 0, 3, 1, 4))
+
+
 def set_packed(flag: Optional[bool]) -> None:
     """Force (True / False) or re-probe (None) the packed-qkv library attention."""
     _PACKED["state"] = flag
