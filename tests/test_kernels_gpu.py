@@ -413,3 +413,36 @@ def test_batchnorm_stacked_views_match_separate_forwards(shape, residual):
     torch.testing.assert_close(net2[0].running_mean, net1[0].running_mean, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(net2[0].running_var, net1[0].running_var, rtol=1e-4, atol=1e-5)
     assert int(net2[0].num_batches_tracked) == int(net1[0].num_batches_tracked) == 2
+
+
+def test_mlm_head_vocab_padding_keeps_loss_and_gradients():
+    """The MLM head pads a vocabulary that is no multiple of 8 with zero-probability classes on CUDA: the
+    distillation loss and the gradients equal those of the unpadded logits."""
+    from argparse import Namespace
+    from tspipe_b200.losses import distil_loss
+    from tspipe_b200.models.bert import BertConfig, MlmHead
+    torch.manual_seed(12)
+    cfg = BertConfig(vocab_size=130, hidden=32, layers=1, heads=4, ffn=64, max_pos=32, dropout=0.0)
+    head_s, head_t = MlmHead(cfg).to(_dev()), MlmHead(cfg).to(_dev())
+    x_s = torch.randn(4, 16, 32, device=_dev(), requires_grad=True)
+    x_t = torch.randn(4, 16, 32, device=_dev())
+    labels = torch.randint(0, 130, (4, 16), device=_dev())
+    labels[:, ::3] = -100
+    attn = torch.ones(4, 16, dtype=torch.long, device=_dev())
+    extra = Namespace(temperature=2.0, alpha_ce=5.0, alpha_mlm=2.0, alpha_cos=1.0)
+    s_out = head_s({"hidden": x_s})
+    with torch.no_grad():
+        t_out = head_t({"hidden": x_t})
+    assert s_out[0].shape[-1] == 136 and t_out[0].shape[-1] == 136
+    loss = distil_loss(s_out, t_out, (labels, attn), None, extra)
+    loss.backward()
+    # unpadded reference in fp32 PyTorch ops
+    xr = x_s.detach().clone().requires_grad_()
+    def plain(head, x):
+        h = head.norm(F.gelu(F.linear(x, head.dense.weight, head.dense.bias)))
+        return F.linear(h, head.decoder.weight, head.decoder.bias), x
+    extra.no_fused = True
+    ref = distil_loss(plain(head_s, xr), tuple(t.detach() for t in plain(head_t, x_t)), (labels, attn), None, extra)
+    ref.backward()
+    torch.testing.assert_close(loss, ref, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(x_s.grad, xr.grad, rtol=1e-2, atol=1e-4)

@@ -747,36 +747,42 @@ class StageEngine:
         given input shape is captured once into a CUDA graph and replayed afterwards: one launch per
         microbatch instead of several hundred (weights are re-cast inside the graph, BatchNorm statistics
         accumulate on the device; only the commit counter lives on the host)."""
-        use_graph = (self.cuda and self.cfg["runtime"].get("cuda_graphs", False) and isinstance(x, torch.Tensor)
+        use_graph = (self.cuda and self.cfg["runtime"].get("cuda_graphs", False)
                      and not any(isinstance(m, nn.Dropout) and m.p > 0 and m.training for m in module.modules()))
         if not use_graph:
             with torch.no_grad(), self._amp():
                 return module(x)
-        key = (tuple(x.shape), x.dtype, x.stride())
+        # stage inputs / outputs may be pytrees (dicts of tensors in the BERT stages): the graph is keyed by the
+        # tensor leaves' geometry and the values of the other leaves, and works on static copies of the tensors
+        leaves, tree, wrapped = pt.flatten(x)
+        tpos = [i for i, l in enumerate(leaves) if isinstance(l, torch.Tensor)]
+        if not tpos or any(not leaves[i].is_cuda for i in tpos):
+            with torch.no_grad(), self._amp():
+                return module(x)
+        key = (str(tree), wrapped, tuple((tuple(leaves[i].shape), leaves[i].dtype, leaves[i].stride()) for i in tpos),
+               tuple(repr(l) for i, l in enumerate(leaves) if i not in tpos))
         entry = self._teacher_graphs.get(key)
         if entry is None or entry[0] < 2:           # two eager calls first (library autotuning, lazy inits)
             self._teacher_graphs[key] = (0 if entry is None else entry[0] + 1, None, None, None)
             with torch.no_grad(), self._amp():
                 return module(x)
         if entry[1] is None:
-            static_in = x.clone()
+            static_leaves = [l.clone() if isinstance(l, torch.Tensor) else l for l in leaves]
+            static_in = pt.unflatten(static_leaves, tree, wrapped)
             graph = torch.cuda.CUDAGraph()
             torch.cuda.current_stream().synchronize()
             with torch.cuda.graph(graph):
                 with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=self.autocast,
                                                      cache_enabled=False):
                     static_out = module(static_in)
-            if not isinstance(static_out, torch.Tensor):
-                self._teacher_graphs[key] = (-10 ** 9, None, None, None)      # pytree outputs: stay eager
-                with torch.no_grad(), self._amp():
-                    return module(x)
-            entry = (2, graph, static_in, static_out)
+            entry = (2, graph, static_leaves, static_out)
             self._teacher_graphs[key] = entry
             # the capture itself did not execute anything: fall through to a replay
-        _, graph, static_in, static_out = entry
-        static_in.copy_(x)
+        _, graph, static_leaves, static_out = entry
+        for i in tpos:
+            static_leaves[i].copy_(leaves[i])
         graph.replay()
-        return static_out.clone()
+        return pt.tree_map_tensors(lambda t: t.clone(), static_out)
 
     def _send_forward(self, op: Op, teacher: bool, outs: List[Any]) -> None:
         net = self._net(teacher)
