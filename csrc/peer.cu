@@ -49,7 +49,28 @@ __global__ void __launch_bounds__(kThreads) dp_reduce_norms_kernel(PeerPtrs grad
   const bool adapt = norms != nullptr && hp[4] != 0.f;
   const float wd = hp[1];
   float sp = 0.f, su = 0.f;
-  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+  // 16-byte peer loads where the chunk starts on a 4-element boundary (flat segments and replica shards do): a
+  // quarter of the round trips over NVLink; the last len % 4 elements (and unaligned chunks) go one by one.
+  const int n4 = (c.begin & 3) == 0 ? c.len >> 2 : 0;
+  for (int i = threadIdx.x; i < n4; i += kThreads) {
+    const int64_t k = c.begin + 4 * (int64_t)i;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) {
+        const float4 t = *reinterpret_cast<const float4*>(grads.p[r] + k);
+        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+      }
+    s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
+    *reinterpret_cast<float4*>(g_out + k) = s;
+    if (adapt) {
+      const float4 a = *reinterpret_cast<const float4*>(p + k);
+      const float ux = s.x + wd * a.x, uy = s.y + wd * a.y, uz = s.z + wd * a.z, uw = s.w + wd * a.w;
+      sp += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      su += ux * ux + uy * uy + uz * uz + uw * uw;
+    }
+  }
+  for (int i = 4 * n4 + threadIdx.x; i < c.len; i += kThreads) {
     const int64_t k = c.begin + i;
     float s = 0.f;
 #pragma unroll
@@ -90,7 +111,23 @@ __global__ void __launch_bounds__(kThreads) dp_lars_apply_kernel(PeerPtrs params
   }
   const float wd_eff = adapt ? wd : 0.f;
   const float* p_self = params.p[self];
-  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+  const int n4 = (c.begin & 3) == 0 ? c.len >> 2 : 0;
+  for (int i = threadIdx.x; i < n4; i += kThreads) {
+    const int64_t k = c.begin + 4 * (int64_t)i;
+    const float4 pv = *reinterpret_cast<const float4*>(p_self + k);
+    const float4 gv = *reinterpret_cast<const float4*>(g + k);
+    float4 mv = *reinterpret_cast<const float4*>(mu + k);
+    mv.x = mom * mv.x + q * (gv.x + wd_eff * pv.x);
+    mv.y = mom * mv.y + q * (gv.y + wd_eff * pv.y);
+    mv.z = mom * mv.z + q * (gv.z + wd_eff * pv.z);
+    mv.w = mom * mv.w + q * (gv.w + wd_eff * pv.w);
+    *reinterpret_cast<float4*>(mu + k) = mv;
+    const float4 np = make_float4(pv.x - lr * mv.x, pv.y - lr * mv.y, pv.z - lr * mv.z, pv.w - lr * mv.w);
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) *reinterpret_cast<float4*>(params.p[r] + k) = np;
+  }
+  for (int i = 4 * n4 + threadIdx.x; i < c.len; i += kThreads) {
     const int64_t k = c.begin + i;
     const float pv = p_self[k];
     const float dp = q * (g[k] + wd_eff * pv);
@@ -113,19 +150,45 @@ __global__ void __launch_bounds__(kThreads) dp_adamw_kernel(PeerPtrs grads, Peer
   const float lr = hp[0], b1 = hp[1], b2 = hp[2], eps = hp[3], wd = hp[4], bc1 = hp[5], bc2 = hp[6];
   const float step = lr / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
   const float* p_self = params.p[self];
-  for (int i = threadIdx.x; i < c.len; i += kThreads) {
+  auto update = [&](float gv, float pv, float& mv, float& vv) -> float {
+    pv *= (1.f - lr * wd);
+    mv = b1 * mv + (1.f - b1) * gv;
+    vv = b2 * vv + (1.f - b2) * gv * gv;
+    return pv - step * mv / (sqrtf(vv) * inv_sqrt_bc2 + eps);
+  };
+  const int n4 = (c.begin & 3) == 0 ? c.len >> 2 : 0;
+  for (int i = threadIdx.x; i < n4; i += kThreads) {
+    const int64_t k = c.begin + 4 * (int64_t)i;
+    float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) {
+        const float4 t = *reinterpret_cast<const float4*>(grads.p[r] + k);
+        gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
+      }
+    const float4 pv = *reinterpret_cast<const float4*>(p_self + k);
+    float4 mv = *reinterpret_cast<const float4*>(m + k), vv = *reinterpret_cast<const float4*>(v + k);
+    float4 np;
+    np.x = update(gv.x * scale, pv.x, mv.x, vv.x);
+    np.y = update(gv.y * scale, pv.y, mv.y, vv.y);
+    np.z = update(gv.z * scale, pv.z, mv.z, vv.z);
+    np.w = update(gv.w * scale, pv.w, mv.w, vv.w);
+    *reinterpret_cast<float4*>(m + k) = mv;
+    *reinterpret_cast<float4*>(v + k) = vv;
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < n_peers) *reinterpret_cast<float4*>(params.p[r] + k) = np;
+  }
+  for (int i = 4 * n4 + threadIdx.x; i < c.len; i += kThreads) {
     const int64_t k = c.begin + i;
     float gv = 0.f;
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
       if (r < n_peers) gv += grads.p[r][k];
-    gv *= scale;
-    float pv = p_self[k] * (1.f - lr * wd);
-    const float mv = b1 * m[k] + (1.f - b1) * gv;
-    const float vv = b2 * v[k] + (1.f - b2) * gv * gv;
+    float mv = m[k], vv = v[k];
+    const float pv = update(gv * scale, p_self[k], mv, vv);
     m[k] = mv;
     v[k] = vv;
-    pv -= step * mv / (sqrtf(vv) * inv_sqrt_bc2 + eps);
 #pragma unroll
     for (int r = 0; r < kMaxPeers; ++r)
       if (r < n_peers) params.p[r][k] = pv;
