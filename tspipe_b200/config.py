@@ -22,6 +22,10 @@ New optional keys (all defaulted so reference YAML files load unchanged):
                              on the first ranks of a replica, student stages on the rest; supervised mode)
 ``runtime.teacher_slots``    batches the split-placement teacher may run ahead (default 2)
 ``runtime.resume``           checkpoint directory (or ``""``) to resume from
+``runtime.fuse_ema``         fold the momentum-teacher update into the optimizer kernel when both are cut alike
+``runtime.merge_views``      single stage, one microbatch: run both views of a network as one stacked forward /
+                             backward with per-view BatchNorm statistics (default True)
+``runtime.cuda_graphs``      replay the teacher's stage forward from a CUDA graph (default False)
 ``runtime.heartbeat_s`` / ``runtime.timeout_s``  failure-detection heartbeat period / deadline
 """
 from __future__ import annotations
