@@ -11,6 +11,7 @@ an ImageFolder tree.
 from __future__ import annotations
 
 import argparse
+import ast
 import os
 import sys
 import time
@@ -51,7 +52,7 @@ def main() -> None:
     with TSPipeProfiler(filename=os.path.join(args.artifact_dir, "profile_out.csv")) as prof:
         tsp = TSPipe(online, target, predictor, optimizer, byol_loss, ema_update, m0, args.artifact_dir, profiler=prof)
         if cfg["trainer"]["dummy_input"]:
-            image = eval(cfg["data_transforms"]["input_shape"])[0]
+            image = ast.literal_eval(cfg["data_transforms"]["input_shape"])[0]
             loader = DummyInputGenerator(bs, input_shape=image, pin=torch.cuda.is_available())
         else:
             from tspipe_b200.datasets import two_crop_imagefolder

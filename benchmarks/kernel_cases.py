@@ -160,7 +160,7 @@ def case_kd():
     s = torch.randn(2048, 1000, device=dev).bfloat16().requires_grad_()
     tt = torch.randn(2048, 1000, device=dev).bfloat16()
     y = torch.randint(0, 1000, (2048,), device=dev)
-    t = _time(lambda: fused.kd_soft_target_loss(s, tt, y, 4.0, 0.9))
+    t = _time(lambda: fused.kd_soft_target_loss(s, tt, y, 4.0, 1.0, 1.0))
     print(f"kd loss [2048,1000] fwd+grad: {t:8.1f} us")
 
 

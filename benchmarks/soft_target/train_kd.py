@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Soft-target knowledge distillation with a frozen teacher (`benchmarks/soft_target/train_kd.py:215-227,
 439-461` in the reference): teacher forward-only, student trained with
-``(1-alpha) * CE + alpha * T^2 * KL(softmax(t/T) || softmax(s/T))`` (`kd_losses/st.py:18-23`).
+``CE + lambda_kd * T^2 * KL(softmax(t/T) || softmax(s/T))`` (`kd_losses/st.py:18-23`, `train_kd.py:448-453`).
 
     torchrun --nproc-per-node 8 benchmarks/soft_target/train_kd.py --tspipe-config benchmarks/soft_target/tspipe.yaml \
         --t-name vit_large --s-name vit_base --batch-size 2048 --dummy
@@ -58,7 +58,7 @@ def main() -> None:
     ap.add_argument("--optimizer", default="adamw", choices=["adamw", "sgd"])
     ap.add_argument("--kd-mode", default="st", choices=["st", "logits"])
     ap.add_argument("--T", type=float, default=4.0)
-    ap.add_argument("--lambda-kd", type=float, default=0.9)
+    ap.add_argument("--lambda-kd", type=float, default=1.0)
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--dummy", action="store_true", default=True)
     ap.add_argument("--artifact-dir", default="runs/soft_target")
@@ -70,7 +70,7 @@ def main() -> None:
     tsp = TSPipe(snet, tnet, None, opt, soft_target_kd if args.kd_mode == "st" else logits_kd, None, 1.0,
                  args.artifact_dir,
                  tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False,
-                 extra_args=Namespace(T=args.T, alpha=args.lambda_kd))
+                 extra_args=Namespace(T=args.T, lambda_kd=args.lambda_kd))
     g = torch.Generator().manual_seed(0)
     img = torch.randn(args.batch_size, 3, args.image, args.image, generator=g)
     lab = torch.randint(0, args.num_class, (args.batch_size,), generator=g)

@@ -206,3 +206,20 @@ def test_vit_convolution_stem_variant():
     x = torch.randn(4, 3, 32, 32)
     assert stem(x).shape == (4, 4, 64)
     assert pred(base(x)).shape == (4, 16)
+
+
+def test_kd_losses_follow_the_reference_weighting():
+    """``CE + lambda_kd * KD`` (`benchmarks/soft_target/train_kd.py:448-453`, ``--lambda_kd`` default 1.0);
+    ``alpha`` selects the convex mix instead."""
+    from argparse import Namespace
+    import torch.nn.functional as F
+    from tspipe_b200.losses import logits_kd, soft_target_kd
+    torch.manual_seed(1)
+    s, t, y = torch.randn(6, 5), torch.randn(6, 5), torch.randint(0, 5, (6,))
+    T = 4.0
+    ce = F.cross_entropy(s, y)
+    kd = F.kl_div(F.log_softmax(s / T, 1), F.softmax(t / T, 1), reduction="batchmean") * T * T
+    torch.testing.assert_close(soft_target_kd(s, t, y, extra_args=Namespace(T=T)), ce + kd)
+    torch.testing.assert_close(soft_target_kd(s, t, y, extra_args=Namespace(T=T, lambda_kd=0.3)), ce + 0.3 * kd)
+    torch.testing.assert_close(soft_target_kd(s, t, y, extra_args=Namespace(T=T, alpha=0.9)), 0.1 * ce + 0.9 * kd)
+    torch.testing.assert_close(logits_kd(s, t, y, extra_args=Namespace(lambda_kd=2.0)), ce + 2.0 * F.mse_loss(s, t))

@@ -32,7 +32,7 @@ def test_watchdog_reports_death_notice_and_silence():
     w = Watchdog(store, 0, 3, heartbeat_s=1, timeout_s=5, progress=lambda: 7, on_failure=failures.append,
                  clock=lambda: now[0])
     w.beat()
-    assert pickle.loads(store.get("hb/0")) == (100.0, 7)
+    assert pickle.loads(store.get("hb/0")) == (100.0, 7, False)
     store.set("hb/1", pickle.dumps((99.9, 1)))
     store.set("hb/2", pickle.dumps((98.0, 1)))
     assert w.check_once() is None
@@ -94,3 +94,23 @@ def test_executor_exception_on_one_rank_stops_all_ranks():
     assert out[1][0] == "failed" and "injected failure" in out[1][2]
     assert out[0][0] == "failed" and ("rank 1 failed" in out[0][2] or "peer" in out[0][2])
     assert out[0][1] < 15 and out[1][1] < 15
+
+
+def test_watchdog_reports_a_rank_that_beats_but_makes_no_progress():
+    """A rank blocked inside a collective keeps its heartbeat thread alive: it is reported once it has stayed busy
+    on the same operation count for the limit; an idle rank (waiting for input) with a constant count is not."""
+    store, now = FakeStore(), [0.0]
+    w = Watchdog(store, 0, 3, heartbeat_s=1, timeout_s=5, progress=lambda: 0, on_failure=lambda e: None,
+                 clock=lambda: now[0], busy=lambda: True)
+    w.beat()
+    assert pickle.loads(store.get("hb/0")) == (0.0, 0, True)
+    for t in (0.0, 2.0, 4.0, 6.0):
+        now[0] = t
+        store.set("hb/1", pickle.dumps((t, 11, True)))       # beating, busy, stuck on op 11
+        store.set("hb/2", pickle.dumps((t, 4, False)))       # beating, idle
+        f = w.check_once()
+        if t <= 4.0:
+            assert f is None
+    assert isinstance(f, PeerFailure) and "rank 1 is stalled" in str(f) and "operation 11" in str(f)
+    store.set("hb/1", pickle.dumps((6.0, 12, True)))         # progress resets the stall clock
+    assert w.check_once() is None

@@ -103,11 +103,11 @@ def test_kd_soft_target_loss(dtype, n, c):
     s = (torch.randn(n, c, device=_dev()) * 2).to(dtype).requires_grad_()
     t = (torch.randn(n, c, device=_dev()) * 2).to(dtype)
     y = torch.randint(0, c, (n,), device=_dev())
-    T, alpha = 4.0, 0.9
-    loss = fused.kd_soft_target_loss(s, t, y, T, alpha)
+    T, lambda_kd = 4.0, 0.7          # the reference's objective: CE + lambda_kd * T^2 * KL
+    loss = fused.kd_soft_target_loss(s, t, y, T, 1.0, lambda_kd)
     loss.backward()
     r = s.detach().float().requires_grad_()
-    ref = (1 - alpha) * F.cross_entropy(r, y) + alpha * T * T * F.kl_div(
+    ref = F.cross_entropy(r, y) + lambda_kd * T * T * F.kl_div(
         F.log_softmax(r / T, 1), F.softmax(t.float() / T, 1), reduction="batchmean")
     ref.backward()
     torch.testing.assert_close(loss, ref.detach(), rtol=2e-4, atol=1e-5)

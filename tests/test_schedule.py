@@ -1,5 +1,12 @@
-"""Schedule goldens (tables dumped from the reference generator, `tspipe/scheduler.py:553-596`)
-and structural properties."""
+"""Schedule goldens and structural properties.
+
+``tests/data/reference_schedule_tables.json`` holds clock-by-clock tables dumped from the reference generator
+(`tspipe/scheduler.py:553-596`) by ``tests/data/dump_reference_schedules.py`` (it imports only the reference's
+scheduler module, with a non-blocking stub for its batch queue).
+
+One deliberate deviation: in the synchronous warm-up batches (``num_skip_initial_staleness``) the reference runs U
+backward items per view (`tspipe/scheduler.py:51-121`), this generator 2U nano-batches as in every other batch;
+the comparison below therefore leaves the backward items of those batches out."""
 import json
 import os
 

@@ -1,8 +1,9 @@
 """Mini-batch / micro-batch containers and the user-overridable scatter/gather pair.
 
 API parity with `tspipe/batch_ops.py`: :class:`Batch` (`:24-149`), :func:`scatter` /
-:func:`gather` (`:168-205`), :class:`ScatterGatherFn` (`:208-221`), :class:`Microbatch`
-(`:239-253`), :class:`BatchList` (`:224-236`), :class:`BatchQueue` (`:256-297`)."""
+:func:`gather` (`:168-205`), :class:`ScatterGatherFn` (`:208-221`), :class:`BatchQueue` (`:256-297`).
+The reference's ``Microbatch`` / ``BatchList`` envelopes (`:224-253`) have no counterpart: a microbatch is identified
+by its position in the schedule (``schedule.Op``: batch, view, microbatch), not by a tagged message."""
 from __future__ import annotations
 
 import threading
@@ -104,21 +105,6 @@ class ScatterGatherFn:
 
 
 defaultScatterGatherFn = ScatterGatherFn(scatter=scatter, gather=gather, batch_size=batch_size)
-
-
-class Microbatch:
-    def __init__(self, batch_id: int, view_id: int, ubatch_id: int, is_target: bool, batch: Optional[Batch]):
-        self.batch_id, self.view_id, self.ubatch_id, self.is_target, self.data = \
-            batch_id, view_id, ubatch_id, is_target, batch
-
-    def __repr__(self) -> str:
-        return (f"Microbatch<batch_id={self.batch_id} view_id={self.view_id} ubatch_id={self.ubatch_id} "
-                f"is_target={self.is_target}>")
-
-
-class BatchList:
-    def __init__(self, batch_id: int, *batches, grad=None):
-        self.batch_id, self.batches, self.grad = batch_id, batches, grad
 
 
 class BatchQueue:

@@ -5,9 +5,9 @@ kernel can simply load from / store to a neighbour's buffer once it is mapped.  
 as a CUDA IPC handle of its allocation plus a byte offset, the handles travel through an object
 collective of the group, and every rank maps its peers' allocations **with its own device current**
 (``csrc/peer.cu: tsp_ipc_import``), which is what makes the pointer valid inside its kernels.
-(A mapping opened under the *owner's* device ordinal - what ``torch.multiprocessing``'s tensor
-rebuilding does - serves library copies but faults when a kernel of another device dereferences it;
-measured on this machine.)  Peers appear as :class:`PeerView` objects: pointer + length, sliceable,
+(CUDA IPC rule: a mapping is usable by kernels of the device that was current when the handle was opened.  A
+mapping opened under the *owner's* device ordinal - what ``torch.multiprocessing``'s tensor rebuilding does -
+serves library copies but faults when a kernel of another device dereferences it.)  Peers appear as :class:`PeerView` objects: pointer + length, sliceable,
 accepted by the kernel bindings wherever a flat tensor is.
 
 The reference moves every such byte with an RPC-negotiated ``dist.send/recv`` pair

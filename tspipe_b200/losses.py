@@ -1,7 +1,10 @@
 """Loss functions with the reference's callback signatures, picklable (module level).
 
-``soft_target_kd``: CE + T^2 * KL(softmax(t/T) || log_softmax(s/T)) batchmean
-(`benchmarks/soft_target/kd_losses/st.py:18-23`, `benchmarks/soft_target/train_kd.py:439-453`).
+``soft_target_kd``: ``CE + lambda_kd * T^2 * KL(softmax(t/T) || log_softmax(s/T))`` (batchmean), the
+reference's objective (`benchmarks/soft_target/kd_losses/st.py:18-23`,
+`benchmarks/soft_target/train_kd.py:439-453`, ``--lambda_kd`` default 1.0); a caller that passes ``alpha``
+instead gets the convex mix ``(1 - alpha) * CE + alpha * T^2 * KL``.  ``logits_kd``: the same with the MSE
+between the logits in place of the KL term (`benchmarks/soft_target/kd_losses/logits.py:17-20`).
 ``byol_loss``: 2 - 2 cos, symmetric, batch mean (`benchmarks/byol/trainer.py:51-55,192-196`).
 ``moco_loss``: InfoNCE with temperature, x 2T, symmetric (`benchmarks/moco-v3/main.py:147-162`).
 ``ema_update``: ``m*t + (1-m)*s`` (`benchmarks/byol/trainer.py:198-212`); it carries the
@@ -25,26 +28,37 @@ def _fused_ok(*ts: torch.Tensor) -> bool:
     return fused.available()
 
 
+def kd_weights(extra_args) -> tuple:
+    """``(w_ce, w_kd)``: ``lambda_kd`` gives the reference's ``CE + lambda_kd * KD`` (default ``lambda_kd = 1``,
+    `benchmarks/soft_target/train_kd.py:62,448-453`); ``alpha`` gives ``(1 - alpha) * CE + alpha * KD``."""
+    if getattr(extra_args, "lambda_kd", None) is not None:
+        return 1.0, float(extra_args.lambda_kd)
+    if getattr(extra_args, "alpha", None) is not None:
+        a = float(extra_args.alpha)
+        return 1.0 - a, a
+    return 1.0, 1.0
+
+
 def soft_target_kd(student_out, teacher_out, labels, args=None, extra_args=None, epoch: int = 0):
     T = float(getattr(extra_args, "T", 4.0))
-    alpha = float(getattr(extra_args, "alpha", getattr(extra_args, "lambda_kd", 0.9)))
+    w_ce, w_kd = kd_weights(extra_args)
     if _fused_ok(student_out, teacher_out) and not getattr(extra_args, "no_fused", False):
         from .ops import fused
-        return fused.kd_soft_target_loss(student_out, teacher_out, labels, T, alpha)
+        return fused.kd_soft_target_loss(student_out, teacher_out, labels, T, w_ce, w_kd)
     ce = F.cross_entropy(student_out.float(), labels)
     kd = F.kl_div(F.log_softmax(student_out.float() / T, dim=1), F.softmax(teacher_out.float() / T, dim=1),
                   reduction="batchmean") * T * T
-    return (1.0 - alpha) * ce + alpha * kd
+    return w_ce * ce + w_kd * kd
 
 
 def logits_kd(student_out, teacher_out, labels, args=None, extra_args=None, epoch: int = 0):
     """"Do deep nets really need to be deep": MSE between student and teacher logits plus CE
     (`benchmarks/soft_target/kd_losses/logits.py:17-20`, `train_kd.py:448-453`)."""
-    lam = float(getattr(extra_args, "lambda_kd", getattr(extra_args, "alpha", 0.9)))
+    w_ce, w_kd = kd_weights(extra_args)
     t = teacher_out if isinstance(teacher_out, torch.Tensor) else None
     if t is None:
         raise TypeError("logits_kd needs the teacher logits as a tensor")
-    return (1.0 - lam) * F.cross_entropy(student_out.float(), labels) + lam * F.mse_loss(student_out.float(), t.float())
+    return w_ce * F.cross_entropy(student_out.float(), labels) + w_kd * F.mse_loss(student_out.float(), t.float())
 
 
 def regression_loss(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:

@@ -217,9 +217,10 @@ def kd_ce_loss(s, t, labels, temp: float, w_ce: float, w_kd: float, row_mask=Non
     return _KdCe.apply(s, t, labels, row_mask, temp, w_ce, w_kd)
 
 
-def kd_soft_target_loss(s, t, labels, temp: float, alpha: float) -> torch.Tensor:
+def kd_soft_target_loss(s, t, labels, temp: float, w_ce: float = 1.0, w_kd: float = 1.0) -> torch.Tensor:
+    """``w_ce * CE(s, labels) + w_kd * T^2 * KL(softmax(t/T) || softmax(s/T))``, both batch means."""
     n = s.shape[0]
-    return kd_ce_loss(s, t, labels, temp, (1.0 - alpha) / n, alpha / n)
+    return kd_ce_loss(s, t, labels, temp, w_ce / n, w_kd / n)
 
 
 def cross_entropy(s, labels) -> torch.Tensor:

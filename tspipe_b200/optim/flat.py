@@ -84,6 +84,35 @@ class _FlatMixin:
     def flat_state_dict(self) -> Dict[str, Any]:
         return {"flat": {k: v.detach().cpu() for k, v in self._flat_state.items()}, "steps": self._steps}
 
+    def shard_range(self) -> Optional[tuple]:
+        """``(lo, hi)``: the range of the flat buffers this replica updates in data-parallel mode (the state
+        outside it is never touched here and stays zero); None when the whole state is local."""
+        if not self.handles_dp or self.flat is None:
+            return None
+        r, idx = self._dp["r"], self._dp["idx"]
+        shard = self.flat.total // r
+        return idx * shard, (idx + 1) * shard
+
+    def flat_shard_state(self) -> Optional[Dict[str, Any]]:
+        """This replica's range of every flat state buffer (for per-replica checkpoint files)."""
+        rng = self.shard_range()
+        if rng is None:
+            return None
+        lo, hi = rng
+        return {"lo": lo, "hi": hi, "total": self.flat.total, "steps": self._steps,
+                "flat": {k: v[lo:hi].detach().cpu().clone() for k, v in self._flat_state.items()}}
+
+    def load_flat_shards(self, pieces: List[Dict[str, Any]]) -> None:
+        """Reassemble the flat state from per-replica ranges (any number of them, any replica count now)."""
+        if self.flat is None:
+            return
+        for piece in pieces:
+            if piece.get("total") != self.flat.total:
+                raise ValueError("optimizer shard was written for a different partition layout")
+            for k, v in piece["flat"].items():
+                self._buf(k)[piece["lo"]: piece["hi"]].copy_(v)
+            self._steps = max(self._steps, int(piece["steps"]))
+
     def state_dict(self):  # type: ignore[override]
         sd = super().state_dict()
         if self.flat is not None:
@@ -91,7 +120,10 @@ class _FlatMixin:
         return sd
 
     def load_state_dict(self, sd):  # type: ignore[override]
-        extra = sd.pop("tspipe_flat", None) if isinstance(sd, dict) else None
+        extra = None
+        if isinstance(sd, dict) and "tspipe_flat" in sd:
+            sd = dict(sd)                      # the caller's dict stays as it was
+            extra = sd.pop("tspipe_flat")
         super().load_state_dict(sd)
         if extra is not None and self.flat is not None:
             for k, v in extra["flat"].items():

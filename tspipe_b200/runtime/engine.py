@@ -304,6 +304,7 @@ class StageEngine:
         self.thread: Optional[threading.Thread] = None
         self.losses: "queue.Queue[Tuple[int, Any]]" = queue.Queue()
         self.op_count = 0
+        self._in_op = False
         self.on_batch_done: Optional[Callable[[int], None]] = None
         self.on_idle: Optional[Callable[[], None]] = None
         self._warm_links()
@@ -389,7 +390,8 @@ class StageEngine:
         if self.topo.world <= 1 or not rt.get("heartbeat_s"):
             return
         self.watchdog = Watchdog(self.topo.store, self.topo.rank, self.topo.world, rt["heartbeat_s"], rt["timeout_s"],
-                                 progress=lambda: self.op_count, on_failure=self._peer_failed)
+                                 progress=lambda: self.op_count, on_failure=self._peer_failed,
+                                 busy=lambda: self._in_op)
         self.watchdog.start()
 
     def _peer_failed(self, exc: BaseException) -> None:
@@ -433,8 +435,13 @@ class StageEngine:
                 except Exception:
                     pass
         finally:
-            if self.watchdog is not None and self.error is None:
-                self.watchdog.stop()
+            if self.watchdog is not None:
+                # an orderly exit says good-bye; after an error the death notice above is what the peers read,
+                # and this rank stops beating either way
+                if self.error is None:
+                    self.watchdog.stop()
+                else:
+                    self.watchdog.halt()
 
     # -- availability ------------------------------------------------------------------------------
     def _pump(self, block: bool) -> bool:
@@ -519,6 +526,13 @@ class StageEngine:
 
     def _dispatch(self, op: Op) -> None:
         self.op_count += 1
+        self._in_op = True
+        try:
+            self._dispatch_op(op)
+        finally:
+            self._in_op = False
+
+    def _dispatch_op(self, op: Op) -> None:
         if op.kind == OpKind.T:
             self._forward(op, teacher=True)
         elif op.kind == OpKind.O:

@@ -168,6 +168,7 @@ class TSPipe:
         self._losses_returned = 0
         self._stopped = False
         self._feed_stream = None
+        self._resumed_batch = 0         # batch id of the checkpoint this run resumed from (0 = fresh run)
 
         if launcher:
             self._init_launcher(device)
@@ -264,6 +265,7 @@ class TSPipe:
             opt = self.optimizer
         self.engine = SplitKDEngine(t, self.config, part, opt, self.loss_fn, self.target_train_mode,
                                     self.scatter_gather_fn, self.args, self.extra_args)
+        self._maybe_resume()
         self.engine.on_batch_done = self._on_batch_done
         self._done_batches = 0
         self.num_ubatches = self.num_bwd_ubatches = self.engine.U
@@ -306,16 +308,24 @@ class TSPipe:
     def _on_batch_done(self, b: int) -> None:
         self._done_batches = b
         every = int(self.config["train"]["save_model_every_iter"] or 0)
-        if every > 0 and b % every == 0 and self.artifact_dir:
+        # Batch ids restart at 1 in a resumed run (the schedule's warm-up phase runs again); checkpoint names and
+        # the batch id stored in them continue from the checkpoint the run started from, so files of the earlier
+        # run are never overwritten and the newest file is always the latest state.
+        gb = b + self._resumed_batch
+        if every > 0 and gb % every == 0 and self.artifact_dir:
             from .ckpt import save_partition
-            save_partition(self.artifact_dir, b, getattr(self.topo, "local", self.topo.stage), self.engine,
-                           replica=self.topo.replica)
+            save_partition(self.artifact_dir, gb, self._partition_id(), self.engine, replica=self.topo.replica)
+
+    def _partition_id(self) -> int:
+        """Index of this rank's partition in checkpoint file names: the stage, or in split placement the rank's
+        position inside its replica (teacher stages first, then student stages)."""
+        return int(getattr(self.topo, "local", self.topo.stage))
 
     def _maybe_resume(self) -> None:
         path = self.config["runtime"]["resume"]
         if path:
             from .ckpt import load_partition
-            self._resumed_batch = load_partition(path, self.topo.stage, self.engine)
+            self._resumed_batch = load_partition(path, self._partition_id(), self.engine)
 
     # ------------------------------------------------------------------------------------------
     # spawn mode
