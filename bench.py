@@ -57,8 +57,8 @@ def parse():
     p.add_argument("--split", default="", help="override model_split, e.g. 9,21/9,17 (online/target)")
     p.add_argument("--trace", action="store_true", help="print per-operation device time totals of the timed pass")
     p.add_argument("--no-peer", action="store_true", help="NCCL all-reduce instead of the peer-memory DP kernels")
-    p.add_argument("--conv1x1", choices=["gemm", "library"], default=None,
-                   help="1x1 convolutions on the tcgen05 GEMM with fused BatchNorm statistics, or the library's")
+    p.add_argument("--conv", choices=["igemm", "library"], default=None,
+                   help="1x1 / 3x3 convolutions on the tcgen05 implicit-GEMM kernels (default) or the library's")
     return p.parse_args()
 
 
@@ -255,9 +255,9 @@ def run_ours(a):
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.backends.cudnn.allow_tf32 = True
 
-    if a.conv1x1 is not None:
+    if a.conv is not None:
         from tspipe_b200.ops import conv as _conv
-        _conv.set_conv1x1(a.conv1x1 == "gemm")
+        _conv.set_igemm(a.conv == "igemm")
     pp, dp, ub, split = default_grid(world)
     if a.pp:
         pp, dp = a.pp, world // a.pp

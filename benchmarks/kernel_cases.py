@@ -10,6 +10,9 @@
     python benchmarks/kernel_cases.py gemm      # tcgen05 GEMM 8192 x 3072 x 768
     python benchmarks/kernel_cases.py infonce   # MoCo InfoNCE forward + backward, 4096 x 256
     python benchmarks/kernel_cases.py attn      # ViT-B attention forward (tcgen05 flash-style kernel)
+    python benchmarks/kernel_cases.py conv [N]  # every 1x1 / 3x3 convolution shape of ResNet-50 (batch N, default 256):
+                                                # implicit-GEMM forward / data grad / weight grad against the library
+    python benchmarks/kernel_cases.py conv1 CIN COUT K STRIDE SIDE [N]   # one convolution shape (profiling)
 
 Each case allocates a few hundred MB at most (inputs larger than the 126 MB L2 where DRAM figures
 matter), runs the op a handful of times and prints CUDA-event timings with the achieved bandwidth.
@@ -244,6 +247,78 @@ def case_attn():
           f"library {tr:7.1f} us")
 
 
+# 1x1 / 3x3 convolutions of ResNet-50 at 224 x 224: (cin, cout, kernel, stride, input side, how many)
+R50_CONV = [(64, 64, 1, 1, 56, 1), (64, 64, 3, 1, 56, 3), (64, 256, 1, 1, 56, 4), (256, 64, 1, 1, 56, 2),
+            (256, 128, 1, 1, 56, 1), (128, 128, 3, 2, 56, 1), (128, 512, 1, 1, 28, 4), (256, 512, 1, 2, 56, 1),
+            (512, 128, 1, 1, 28, 3), (128, 128, 3, 1, 28, 3),
+            (512, 256, 1, 1, 28, 1), (256, 256, 3, 2, 28, 1), (256, 1024, 1, 1, 14, 6), (512, 1024, 1, 2, 28, 1),
+            (1024, 256, 1, 1, 14, 5), (256, 256, 3, 1, 14, 5),
+            (1024, 512, 1, 1, 14, 1), (512, 512, 3, 2, 14, 1), (512, 2048, 1, 1, 7, 3), (1024, 2048, 1, 2, 14, 1),
+            (2048, 512, 1, 1, 7, 2), (512, 512, 3, 1, 7, 2)]
+
+
+def _conv_one(cin, cout, k, stride, side, n, flush):
+    """(own fprop, own dgrad, own wgrad, library fprop, library dgrad + wgrad) in microseconds, and the FLOPs of one
+    of the three products."""
+    import torch.nn.functional as F
+    from tspipe_b200.ops import conv, gemm
+    dev = torch.device("cuda")
+    pad = (k - 1) // 2
+    x = torch.randn(n, cin, side, side, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    wgt = (torch.randn(cout, cin, k, k, device=dev) * 0.05).to(memory_format=torch.channels_last)
+    w16 = wgt.to(torch.bfloat16)
+    xg = x.clone().requires_grad_()
+    wp = wgt.clone().requires_grad_()
+    y, _ = conv.conv2d(xg, wp, stride, want_sums=True, segments=2)
+    g = torch.randn_like(y)
+    so = side // stride
+    flops = 2.0 * n * so * so * cout * cin * k * k
+    t_f = _time(lambda: conv.conv2d(x, wgt, stride, want_sums=True, segments=2), flush=flush)
+    L = conv._lib()
+    import ctypes as C
+    from tspipe_b200.ops import fused as f
+    st = f._ptr(gemm._status_word(dev))
+    dx = torch.empty_like(x)
+    dw = torch.zeros(cout, k, k, cin, device=dev)
+    w16k = conv._w16(wgt)
+    args = (C.c_int(n), C.c_int(side), C.c_int(side), C.c_int(cin), C.c_int(cout), C.c_int(k), C.c_int(stride))
+    t_d = _time(lambda: L.tsp_conv_dgrad(f._ptr(g), f._ptr(w16k), f._ptr(dx), *args, st, f._stream()), flush=flush)
+    t_w = _time(lambda: L.tsp_conv_wgrad(f._ptr(x), f._ptr(g), f._ptr(dw), *args, st, f._stream()), flush=flush)
+    gemm.check_status()
+    t_lf = _time(lambda: F.conv2d(x, w16, stride=stride, padding=pad), flush=flush)
+    t_lb = _time(lambda: torch.ops.aten.convolution_backward(g, x, w16, None, [stride, stride], [pad, pad], [1, 1], False,
+                                                             [0, 0], 1, [True, True, False]), flush=flush)
+    return t_f, t_d, t_w, t_lf, t_lb, flops
+
+
+def case_conv():
+    n = int(sys.argv[2]) if len(sys.argv) > 2 else 256
+    torch.backends.cudnn.benchmark = True
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    tot = [0.0] * 5
+    print(f"ResNet-50 convolutions, batch {n}, bf16 channels-last; times in us (own kernels: forward incl. BatchNorm "
+          "statistics of two view segments | data grad | weight grad; library: forward | data + weight grad)")
+    for cin, cout, k, stride, side, count in R50_CONV:
+        t_f, t_d, t_w, t_lf, t_lb, flops = _conv_one(cin, cout, k, stride, side, n, flush)
+        for i, t in enumerate((t_f, t_d, t_w, t_lf, t_lb)):
+            tot[i] += t * count
+        print(f"{cin:5d}->{cout:5d} k{k} s{stride} @{side:3d} x{count}: own {t_f:7.1f} {t_d:7.1f} {t_w:7.1f} "
+              f"({flops / t_f / 1e6:6.0f} {flops / t_d / 1e6:6.0f} {flops / t_w / 1e6:6.0f} TFLOP/s) | library {t_lf:7.1f} "
+              f"{t_lb:7.1f}", flush=True)
+    print(f"sum over the network: own fwd {tot[0] / 1e3:.2f} ms, dgrad {tot[1] / 1e3:.2f} ms, wgrad {tot[2] / 1e3:.2f} ms; "
+          f"library fwd {tot[3] / 1e3:.2f} ms, bwd {tot[4] / 1e3:.2f} ms")
+
+
+def case_conv1():
+    cin, cout, k, stride, side = (int(v) for v in sys.argv[2:7])
+    n = int(sys.argv[7]) if len(sys.argv) > 7 else 256
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    t_f, t_d, t_w, t_lf, t_lb, flops = _conv_one(cin, cout, k, stride, side, n, flush)
+    print(f"{cin}->{cout} k{k} s{stride} @{side} batch {n}: own fwd {t_f:.1f} us ({flops / t_f / 1e6:.0f} TFLOP/s), dgrad "
+          f"{t_d:.1f} us ({flops / t_d / 1e6:.0f}), wgrad {t_w:.1f} us ({flops / t_w / 1e6:.0f}); library fwd {t_lf:.1f} us, "
+          f"bwd {t_lb:.1f} us")
+
+
 if __name__ == "__main__":
     {"bn": case_bn, "bn_r50": case_bn_r50, "stem": case_stem, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
-     "infonce": case_infonce, "attn": case_attn}[sys.argv[1]]()
+     "infonce": case_infonce, "attn": case_attn, "conv": case_conv, "conv1": case_conv1}[sys.argv[1]]()

@@ -1,4 +1,5 @@
-"""tcgen05 stem convolution (7 x 7 / 2, 3 -> 64) and fused partition execution against plain PyTorch in fp32."""
+"""tcgen05 convolutions (stem 7 x 7 / 2, implicit-GEMM 1x1 / 3x3) and fused partition execution against plain PyTorch
+in fp32."""
 import copy
 
 import pytest
@@ -81,56 +82,77 @@ def test_stem_conv_statistics_per_group_of_images():
         torch.testing.assert_close(sums[g, 64:], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=1e-2)
 
 
-@pytest.mark.parametrize("shape,cout,segs", [((4, 64, 16, 16), 256, 1), ((8, 256, 8, 8), 64, 2), ((2, 512, 16, 8), 1024, 2),
-                                             ((6, 128, 16, 16), 520, 1)])
-@pytest.mark.parametrize("pair", [False, True])
-def test_conv1x1_gemm_with_batchnorm_statistics(shape, cout, segs, pair):
-    """1 x 1 convolution on the tcgen05 GEMM: output, per-group column statistics and gradients vs F.conv2d."""
+# (input shape NCHW, cout, kernel, stride, segments)
+IGEMM_CASES = [
+    ((4, 64, 16, 16), 256, 1, 1, 1),      # 1x1: plain GEMM over 1024 pixels
+    ((8, 256, 8, 8), 64, 1, 1, 2),        # narrow output, two view segments
+    ((3, 128, 10, 10), 64, 1, 1, 1),      # 300 pixels: ragged last tile (no statistics possible)
+    ((4, 64, 14, 14), 64, 3, 1, 2),       # 3x3: boxes of 14 x 7 pixels, odd number of (tap, ci) blocks
+    ((2, 64, 9, 9), 128, 3, 1, 1),        # odd width: 81-pixel boxes (zero rows in the weight-gradient K loop)
+    ((8, 128, 7, 7), 128, 3, 1, 2),       # 7 x 7 images: two images per box
+    ((2, 64, 12, 12), 128, 3, 2, 1),      # stride 2 through the parity views
+    ((2, 128, 56, 56), 128, 3, 2, 2),     # ResNet-50 layer2 shape: 28 x 4 boxes
+    ((2, 128, 8, 8), 256, 1, 2, 1),       # 1x1 stride 2 (downsample branch)
+    ((2, 256, 56, 56), 64, 1, 1, 2),      # ResNet-50 layer1 conv1
+    ((2, 512, 16, 8), 1024, 1, 1, 2),
+    ((1, 64, 130, 6), 64, 3, 1, 1),       # wider than one box
+]
+
+
+@pytest.mark.parametrize("shape,cout,k,stride,segs", IGEMM_CASES)
+def test_igemm_convolution_forward_backward_and_statistics(shape, cout, k, stride, segs):
+    """Implicit-GEMM convolution on tcgen05: output, per-segment channel statistics, data and weight gradient against
+    F.conv2d in fp32 (same bf16-rounded operands)."""
     from tspipe_b200.ops import conv, gemm
     torch.manual_seed(3)
     dev = torch.device("cuda", 0)
     x = torch.randn(shape, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last).requires_grad_()
-    m = nn.Conv2d(shape[1], cout, 1, bias=False).to(dev)
-    conv._MIN_COUT = 64
-    try:
-        assert conv.conv1x1_eligible(m, x, segs)
-    finally:
-        conv._MIN_COUT = 256
+    m = nn.Conv2d(shape[1], cout, k, stride=stride, padding=(k - 1) // 2, bias=False).to(dev)
+    m = m.to(memory_format=torch.channels_last)
+    assert conv.igemm_eligible(m, x)
     conv.clear_weight_cache()
-    conv._PAIR = pair
-    try:
-        y, sums = conv.conv1x1(x, m.weight, segs)
-    finally:
-        conv._PAIR = False
+    y, sums = conv.conv2d(x, m.weight, stride, want_sums=True, segments=segs)
     gemm.check_status()
     xr = x.detach().float().requires_grad_()
     wr = m.weight.detach().bfloat16().float().requires_grad_()
-    ref = F.conv2d(xr, wr)
+    ref = F.conv2d(xr, wr, stride=stride, padding=(k - 1) // 2)
+    assert y.shape == ref.shape and y.is_contiguous(memory_format=torch.channels_last)
     torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
     yf = y.float()
-    sums = sums.view(segs, 2, cout)
-    for g, part in enumerate(yf.chunk(segs)):
-        torch.testing.assert_close(sums[g, 0], part.sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
-        torch.testing.assert_close(sums[g, 1], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
+    if sums is not None:
+        sums = sums.view(segs, 2, cout)
+        for g, part in enumerate(yf.chunk(segs)):
+            torch.testing.assert_close(sums[g, 0], part.sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
+            torch.testing.assert_close(sums[g, 1], (part * part).sum((0, 2, 3)), rtol=1e-3, atol=2e-2)
+    else:
+        pixels = shape[0] // segs * ref.shape[2] * ref.shape[3]
+        assert k == 1 and stride == 1 and pixels % 128 != 0     # the only case without statistics: ragged 1x1 tiles
     g = torch.randn_like(y)
     y.backward(g)
+    gemm.check_status()
     ref.backward(g.float())
-    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2 * max(xr.grad.abs().max().item(), 1.0))
     torch.testing.assert_close(m.weight.grad, wr.grad, rtol=5e-2, atol=5e-2 * wr.grad.abs().max().item())
+    # a second backward ADDS into the existing fp32 gradient (the kernel accumulates in place)
+    y2, _ = conv.conv2d(x, m.weight, stride)
+    y2.backward(g)
+    gemm.check_status()
+    torch.testing.assert_close(m.weight.grad, 2 * wr.grad, rtol=5e-2, atol=1e-1 * wr.grad.abs().max().item())
 
 
-def test_bottleneck_with_gemm_convolutions_matches_library_path():
+def test_bottleneck_on_igemm_convolutions_matches_library_path():
     from tspipe_b200.batchnorm import DeferredBatchNorm
     from tspipe_b200.models.resnet import Bottleneck
     from tspipe_b200.ops import conv, gemm
     torch.manual_seed(4)
     dev = torch.device("cuda", 0)
-    blk = DeferredBatchNorm.convert_deferred_batch_norm(Bottleneck(256, 64), chunks=10 ** 9).to(dev)   # conv3: 64 -> 256
+    down = nn.Sequential(nn.Conv2d(256, 512, 1, stride=2, bias=False), nn.BatchNorm2d(512))
+    blk = DeferredBatchNorm.convert_deferred_batch_norm(Bottleneck(256, 128, 2, down), chunks=10 ** 9).to(dev)
     blk = blk.to(memory_format=torch.channels_last)
     x = torch.randn(8, 256, 16, 16, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
     outs, grads = [], []
     for flag in (False, True):
-        conv.set_conv1x1(flag)
+        conv.set_igemm(flag)
         conv.clear_weight_cache()
         try:
             xi = x.clone().requires_grad_()
@@ -139,7 +161,7 @@ def test_bottleneck_with_gemm_convolutions_matches_library_path():
                 y = blk(xi)
             y.float().square().mean().backward()
         finally:
-            conv.set_conv1x1(False)
+            conv.set_igemm(True)
         outs.append(y.float())
         grads.append([xi.grad.float()] + [p.grad.clone() for p in blk.parameters()])
     gemm.check_status()

@@ -114,3 +114,31 @@ def test_watchdog_reports_a_rank_that_beats_but_makes_no_progress():
     assert isinstance(f, PeerFailure) and "rank 1 is stalled" in str(f) and "operation 11" in str(f)
     store.set("hb/1", pickle.dumps((6.0, 12, True)))         # progress resets the stall clock
     assert w.check_once() is None
+
+
+@pytest.mark.gpu
+def test_device_side_bounded_wait_gives_up_and_reports():
+    """A kernel waits on an mbarrier that nothing completes (the signal is simply never sent).  The bounded wait of
+    the tcgen05 kernels gives up after its limit, writes its code into the status word and the kernel returns: no
+    trap, no hang, and the next kernel on the same context runs normally."""
+    import ctypes as C
+    from tspipe_b200.ops import conv, fused as f, gemm
+    dev = torch.device("cuda", 0)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    L = conv._lib()
+    L.tsp_bounded_wait_probe.restype = C.c_int
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.device(dev):
+        e0.record()
+        assert L.tsp_bounded_wait_probe(C.c_int(50), C.c_int(7), f._ptr(status), f._stream()) == 0
+        e1.record()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 7
+    assert 40.0 <= e0.elapsed_time(e1) <= 500.0
+    # the context is intact: a tensor-core convolution right after gives the right answer
+    x = torch.randn(2, 64, 8, 8, device=dev).to(dtype=torch.bfloat16, memory_format=torch.channels_last)
+    w = torch.randn(64, 64, 1, 1, device=dev) * 0.1
+    y, _ = conv.conv2d(x, w)
+    gemm.check_status()
+    ref = torch.nn.functional.conv2d(x.float(), w.bfloat16().float())
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)

@@ -14,9 +14,15 @@ from typing import Optional
 import torch
 from torch import nn
 
-from ..ops.bn import bn_act
 from ..ops.conv import conv_bn_act
 from ..ops.pool import MaxPool3x3s2
+
+
+def _downsample(down: nn.Module, x: torch.Tensor) -> torch.Tensor:
+    """The projection shortcut (1x1 convolution + BatchNorm) through the fused convolution path."""
+    if isinstance(down, nn.Sequential) and len(down) == 2 and isinstance(down[0], nn.Conv2d):
+        return conv_bn_act(down[0], down[1], x)
+    return down(x)
 
 
 class Bottleneck(nn.Module):
@@ -34,9 +40,9 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        identity = x if self.downsample is None else self.downsample(x)
+        identity = x if self.downsample is None else _downsample(self.downsample, x)
         out = conv_bn_act(self.conv1, self.bn1, x, relu=True)
-        out = bn_act(self.bn2, self.conv2(out), relu=True)
+        out = conv_bn_act(self.conv2, self.bn2, out, relu=True)
         return conv_bn_act(self.conv3, self.bn3, out, residual=identity, relu=True)
 
 
@@ -53,9 +59,9 @@ class BasicBlock(nn.Module):
         self.downsample = downsample
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        identity = x if self.downsample is None else self.downsample(x)
-        out = bn_act(self.bn1, self.conv1(x), relu=True)
-        return bn_act(self.bn2, self.conv2(out), residual=identity, relu=True)
+        identity = x if self.downsample is None else _downsample(self.downsample, x)
+        out = conv_bn_act(self.conv1, self.bn1, x, relu=True)
+        return conv_bn_act(self.conv2, self.bn2, out, residual=identity, relu=True)
 
 
 class Reshape2d(nn.Module):
