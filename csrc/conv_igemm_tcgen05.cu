@@ -51,7 +51,8 @@ namespace {
 
 using namespace tc5;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;           // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM lane quarter)
+constexpr int kWgThreads = 192;         // weight gradient: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int kBoxBytes = 128 * 128;        // shared memory reserved per pixel box: 128 rows x 64 bf16
 constexpr int kMaxTaps = 9;
 
@@ -62,6 +63,8 @@ struct Geom {
   int row_pitch;                            // accumulator rows per box row: box_w, or box_w + 2 in the halo kernel
   int pix;                                  // row_pitch * box_h * box_n  (<= 128): accumulator rows in use
   int halo_rows;                            // halo kernel: (box_w + 2) * (box_h + 2) rows fetched per channel block
+  int b_resident;                           // halo kernel: the nine weight tiles are loaded once and stay
+  int tma_store;                            // forward kernel, flat pixel grid: the epilogue writes with TMA stores
   unsigned long long wait_ns;               // give-up time of every mbarrier wait
   int n_taps;
   int kc;                                   // channels per tap on the contraction side (forward) / on the M side (wgrad)
@@ -82,11 +85,20 @@ struct FwdCfg {
   static constexpr int kABytes = kBoxBytes;
   static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 5 : 6);
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kGroup = 2;                          // stages released per tcgen05.commit (a commit costs the
+  static constexpr int kGroups = kStages / kGroup;          // issuing thread about as much as eight MMAs)
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kStoreBytes = 4 * 32 * 128;          // one 32-row x 128-byte staging block per epilogue warp
+  static constexpr int kStoreBytes = 8 * 32 * 128;          // one 32-row x 128-byte staging block per epilogue warp
   static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
 };
+
+// Tiles are dealt to the CTAs in contiguous ranges (tile index = n_tile * tiles_m + m_tile): a CTA then stays on one
+// block of output channels - one set of weights, one set of statistics accumulators - for nearly all of its tiles,
+// and consecutive tiles are neighbouring pixel boxes.
+__device__ __forceinline__ int tile_begin(int num_tiles, unsigned cta) {
+  return (int)((long long)num_tiles * cta / gridDim.x);
+}
 
 __device__ __forceinline__ void tile_origin(const Geom& g, int tm, int& w0, int& h0, int& n0) {
   const int wb = tm % g.tiles_w, r = tm / g.tiles_w;
@@ -95,18 +107,22 @@ __device__ __forceinline__ void tile_origin(const Geom& g, int tm, int& w0, int&
   n0 = (r / g.tiles_h) * g.box_n;
 }
 
-// Epilogue warps (2..5) of the forward / data-gradient kernels.  Accumulator row p of a tile is pixel
+// Epilogue warps (2..9) of the forward / data-gradient kernels.  A tile has `n_sub` accumulators of 128 rows (SUBS
+// reserved per TMEM buffer); accumulator row p of the tile (p = 128 * sub + TMEM lane) is pixel
 // (p % row_pitch, (p / row_pitch) % box_h, p / (row_pitch * box_h)) of the tile's box; rows in border columns, past
-// the box or outside the image are not stored.  Per 64-channel block: TMEM -> registers -> bf16 -> swizzled shared
-// memory (rows that are not stored are written as zeros) -> per-channel sums from shared memory (STATS) and coalesced
-// 16-byte stores, 8 lanes per pixel.
-template <int BN, bool STATS>
-__device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int tiles_m, uint32_t tmem_base,
+// the box or outside the image are not stored.  Warp w owns TMEM lanes 32 * (w % 4) .. + 31; the two warps that share
+// a lane quarter split the (accumulator, 64-channel block) units between them.  Per unit: TMEM -> registers -> bf16
+// -> swizzled shared memory (rows that are not stored are written as zeros) -> per-channel sums from shared memory
+// (STATS) and coalesced 16-byte stores, 8 lanes per pixel.
+template <int BN, int SUBS, int ACC_BUFS, bool STATS>
+__device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int tiles_m, int n_sub, uint32_t tmem_base,
                                              uint64_t* tmem_full_bar, uint64_t* tmem_empty_bar, uint8_t* store_bufs,
                                              __nv_bfloat16* __restrict__ out, float* __restrict__ col_sums,
-                                             int* __restrict__ status, int warp, int lane) {
-  const int quarter = warp & 3;
-  uint8_t* buf = store_bufs + quarter * (32 * 128);
+                                             int* __restrict__ status, int warp, int lane,
+                                             const CUtensorMap* __restrict__ omap = nullptr) {
+  const int quarter = warp & 3, group = (warp - 2) >> 2;
+  const bool tma_out = omap != nullptr && g.tma_store != 0;       // flat pixel grid: 32-row blocks go out as TMA stores
+  uint8_t* buf = store_bufs + (warp - 2) * (32 * 128);
   uint32_t lt = 0;
   bool ok = true;
   constexpr int kStatBlocks = BN / 64;
@@ -120,7 +136,8 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
 #pragma unroll
       for (int i = 0; i < kStatBlocks; ++i) {
         const int col = cur_c0 + 64 * i + 2 * lane;
-        if (col < g.nc) {                       // nc is even: columns col and col + 1 exist together
+        // (the blocks of the other warp of this lane quarter hold zeros here; nc is even: col and col + 1 exist together)
+        if (col < g.nc && (cs[i][1] != 0.f || cs[i][3] != 0.f)) {
           atomicAdd(dst + col, cs[i][0]); atomicAdd(dst + g.nc + col, cs[i][1]);
           atomicAdd(dst + col + 1, cs[i][2]); atomicAdd(dst + g.nc + col + 1, cs[i][3]);
         }
@@ -128,71 +145,89 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
       }
     }
   };
-  for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+  const int t_begin = tile_begin(num_tiles, blockIdx.x), t_end = tile_begin(num_tiles, blockIdx.x + 1);
+  for (int t = t_begin; t < t_end && ok; ++t, ++lt) {
     int w0, h0, n0;
     tile_origin(g, t % tiles_m, w0, h0, n0);
     const int c0 = (t / tiles_m) * BN;
-    const uint32_t acc = lt & 1, use = lt >> 1;
+    const uint32_t acc = lt % ACC_BUFS, use = lt / ACC_BUFS;
     if (STATS) {
       const int seg = (int)((((int64_t)n0 * g.out_h + h0) * g.out_w + w0) / g.rows_per_seg);
       if (c0 != cur_c0 || seg != cur_seg) { flush_stats(); cur_c0 = c0; cur_seg = seg; }
     }
-    // this lane's pixel and where it is stored (units of 8 elements), -1 for rows that are not stored
-    int row_off = -1;
-    {
-      const int p = quarter * 32 + lane;
-      const int bw = p % g.row_pitch, r2 = p / g.row_pitch;
-      const int w = w0 + bw, h = h0 + r2 % g.box_h, n = n0 + r2 / g.box_h;
-      if (p < g.pix && bw < g.box_w && w < g.out_w && h < g.out_h && n < g.out_n)
-        row_off = n * g.out_sn + h * g.out_sh + w * g.out_sw;
-    }
-    ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3, g.wait_ns));
+    ok = mbar_wait_warp(tmem_full_bar + acc, use & 1, status, 3, g.wait_ns, lane);
     if (!ok) break;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < kStatBlocks; ++i) {
-      const int col = c0 + 64 * i;
-      if (col < g.nc) {
-        uint32_t r[64];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)(64 * i);
-        tmem_ld_32x32_issue(taddr, r);
-        tmem_ld_32x32_issue(taddr + 32, r + 32);
-        tmem_ld_wait();
-        uint8_t* my_row = buf + lane * 128;
-        const bool keep = row_off >= 0;
+    for (int sub = 0; sub < SUBS; ++sub) {
+      if (sub < n_sub) {
+        // this lane's pixel and where it is stored (units of 8 elements), -1 for rows that are not stored
+        int row_off = -1;
+        {
+          const int p = sub * 128 + quarter * 32 + lane;
+          const int bw = p % g.row_pitch, r2 = p / g.row_pitch;
+          const int w = w0 + bw, h = h0 + r2 % g.box_h, n = n0 + r2 / g.box_h;
+          if (p < g.pix && bw < g.box_w && w < g.out_w && h < g.out_h && n < g.out_n)
+            row_off = n * g.out_sn + h * g.out_sh + w * g.out_sw;
+        }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {             // 16-byte piece j of this row sits at piece (j ^ (row & 7))
-          uint4 q = make_uint4(0u, 0u, 0u, 0u);
-          if (keep) {
-            q.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-            q.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-            q.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-            q.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        for (int i = 0; i < kStatBlocks; ++i) {
+          const int col = c0 + 64 * i;
+          constexpr int kUnits = SUBS * kStatBlocks;
+          const bool mine = kUnits == 1 ? group == 0 : ((sub * kStatBlocks + i) & 1) == group;
+          if (mine && col < g.nc) {
+            uint32_t r[64];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (acc * SUBS + sub) * BN + (uint32_t)(64 * i);
+            tmem_ld_32x32_issue(taddr, r);
+            tmem_ld_32x32_issue(taddr + 32, r + 32);
+            tmem_ld_wait();
+            uint8_t* my_row = buf + lane * 128;
+            const bool keep = row_off >= 0;
+            if (tma_out) {             // the previous block's store has finished reading the staging buffer
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {         // 16-byte piece j of this row sits at piece (j ^ (row & 7))
+              uint4 q = make_uint4(0u, 0u, 0u, 0u);
+              if (keep) {
+                q.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                q.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                q.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                q.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              }
+              *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = q;
+            }
+            __syncwarp();
+            if (STATS) {
+              // column sums of the rounded block (rows that are not stored hold zeros): this lane owns columns
+              // 2 * lane and 2 * lane + 1
+#pragma unroll
+              for (int rr = 0; rr < 32; ++rr) {
+                const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                                       (lane & 3) * 4);
+                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
+                cs[i][0] += f.x; cs[i][1] = fmaf(f.x, f.x, cs[i][1]); cs[i][2] += f.y; cs[i][3] = fmaf(f.y, f.y, cs[i][3]);
+              }
+            }
+            if (tma_out) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) tma_store_2d(omap, buf, col, w0 + sub * 128 + quarter * 32);   // rows past the end are clipped
+            } else {
+              // coalesced stores: 8 lanes write the 128 bytes of one pixel's channel block, 4 pixels per instruction
+              const int pc = lane & 7;
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int rr = 4 * k + (lane >> 3);
+                const int off = __shfl_sync(0xffffffffu, row_off, rr);
+                const uint4 q = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((pc ^ (rr & 7)) << 4));
+                if (off >= 0) *reinterpret_cast<uint4*>(out + ((int64_t)off << 3) + col + pc * 8) = q;
+              }
+              __syncwarp();
+            }
           }
-          *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = q;
         }
-        __syncwarp();
-        if (STATS) {
-          // column sums of the rounded block (rows that are not stored hold zeros): this lane owns columns
-          // 2 * lane and 2 * lane + 1
-#pragma unroll
-          for (int rr = 0; rr < 32; ++rr) {
-            const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
-                                                                   (lane & 3) * 4);
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
-            cs[i][0] += f.x; cs[i][1] = fmaf(f.x, f.x, cs[i][1]); cs[i][2] += f.y; cs[i][3] = fmaf(f.y, f.y, cs[i][3]);
-          }
-        }
-        // coalesced stores: 8 lanes write the 128 bytes of one pixel's channel block, 4 pixels per instruction
-        const int pc = lane & 7;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int rr = 4 * k + (lane >> 3);
-          const int off = __shfl_sync(0xffffffffu, row_off, rr);
-          const uint4 q = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((pc ^ (rr & 7)) << 4));
-          if (off >= 0) *reinterpret_cast<uint4*>(out + ((int64_t)off << 3) + col + pc * 8) = q;
-        }
-        __syncwarp();
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -200,6 +235,10 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
     if (lane == 0) mbar_arrive(tmem_empty_bar + acc);
   }
   if (STATS) flush_stats();
+  if (tma_out) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // staging buffer free, stores complete
+    __syncwarp();
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -208,8 +247,8 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
 template <int BN, bool B_MN, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ CUtensorMap wmap,
-                const __grid_constant__ Geom g, __nv_bfloat16* __restrict__ out, float* __restrict__ col_sums,
-                int* __restrict__ status) {
+                const __grid_constant__ CUtensorMap omap, const __grid_constant__ Geom g, __nv_bfloat16* __restrict__ out,
+                float* __restrict__ col_sums, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   using C = FwdCfg<BN>;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -234,7 +273,7 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar + a, 1);
-      mbar_init(tmem_empty_bar + a, 4);
+      mbar_init(tmem_empty_bar + a, 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&amaps.m[0]) : "memory");
@@ -257,7 +296,7 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
       uint32_t it = 0;
       bool ok = true;
       const uint32_t tx = (uint32_t)(g.pix * 128 + C::kBBytes);     // a box is written in full, zero fill included
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = tile_begin(num_tiles, blockIdx.x); t < tile_begin(num_tiles, blockIdx.x + 1) && ok; ++t) {
         int w0, h0, n0;
         tile_origin(g, t % tiles_m, w0, h0, n0);
         const int c0 = (t / tiles_m) * BN;
@@ -266,8 +305,10 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
           const int xw = w0 + g.tap_dw[tap], xh = h0 + g.tap_dh[tap], wcol = g.tap_col[tap];
           for (int cb = 0; cb < kcb; ++cb, ++it) {
             const int s = it % C::kStages;
-            const uint32_t round = it / C::kStages;
-            if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+            if (it % C::kGroup == 0) {              // first stage of a group: the whole group must have been released
+              const uint32_t grp = (it / C::kGroup) % C::kGroups, round = (it / C::kGroup) / C::kGroups;
+              if (round > 0 && !mbar_wait_parked(empty_bar + grp, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+            }
             uint8_t* a_dst = tiles + s * C::kStageBytes;
             uint8_t* b_dst = a_dst + C::kABytes;
             mbar_expect_tx(full_bar + s, tx);
@@ -287,9 +328,10 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(128, BN, false, B_MN);
+      const uint32_t tiles_addr = smem_u32(tiles);
       uint32_t it = 0, lt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+      for (int t = tile_begin(num_tiles, blockIdx.x); t < tile_begin(num_tiles, blockIdx.x + 1) && ok; ++t, ++lt) {
         const uint32_t acc = lt & 1, use = lt >> 1;
         if (use > 0) {
           ok = mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4, g.wait_ns);
@@ -297,28 +339,29 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accum = 0u;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % C::kStages;
           const uint32_t round = it / C::kStages;
           ok = mbar_wait(full_bar + s, round & 1, status, 2, g.wait_ns);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-          const uint32_t b_addr = a_addr + C::kABytes;
-          const uint64_t a_desc = desc_k_major(a_addr);
+          const uint32_t a_addr = tiles_addr + s * C::kStageBytes;
+          const uint32_t a_lo = desc_lo_k_major(a_addr);
+          const uint32_t b_lo = B_MN ? desc_lo_mn_major(a_addr + C::kABytes, 8192) : desc_lo_k_major(a_addr + C::kABytes);
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t b_desc = B_MN ? desc_mn_major(b_addr + kk * 2048, 8192) : desc_k_major(b_addr) + (uint64_t)(2 * kk);
-            umma_bf16(d_tmem, a_desc + (uint64_t)(2 * kk), b_desc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {          // 16 along K: +32 bytes in a K-major row, +2048 bytes (16 rows) MN-major
+            umma_bf16_lo(d_tmem, a_lo + 2 * kk, b_lo + (B_MN ? 128 * kk : 2 * kk), idesc, accum);
+            accum = 1u;
           }
-          umma_commit(empty_bar + s);
+          if (it % C::kGroup == C::kGroup - 1) umma_commit(empty_bar + (it / C::kGroup) % C::kGroups);
         }
         umma_commit(tmem_full_bar + acc);
       }
     }
   } else {
-    fwd_epilogue<BN, STATS>(g, num_tiles, tiles_m, tmem_base, tmem_full_bar, tmem_empty_bar, store_bufs, out, col_sums,
-                            status, warp, lane);
+    fwd_epilogue<BN, 1, 2, STATS>(g, num_tiles, tiles_m, 1, tmem_base, tmem_full_bar, tmem_empty_bar, store_bufs, out,
+                                  col_sums, status, warp, lane, &omap);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -333,23 +376,26 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
 // ---------------------------------------------------------------------------------------------------------------
 template <int BN>
 struct HaloCfg {
-  static constexpr int kABytes = 256 * 128;                   // bordered box: up to 256 rows of 64 channels
-  static constexpr int kAStages = BN == 256 ? 2 : 3;
+  static constexpr int kARows = 384;                          // bordered box: up to 256 accumulator rows + 2 rows + 2
+  static constexpr int kABytes = kARows * 128;
+  static constexpr int kAStages = 2;
   static constexpr int kBBytes = BN * 128;                    // weights of one tap and one 64-channel block
-  static constexpr int kBStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kStoreBytes = 4 * 32 * 128;
+  static constexpr int kBStages = BN == 64 ? 9 : (BN == 128 ? 6 : 3);
+  static constexpr int kBGroup = BN == 256 ? 1 : 3;           // weight stages released per tcgen05.commit
+  static constexpr int kBGroups = kBStages / kBGroup;
+  static constexpr int kAccBufs = BN == 256 ? 1 : 2;          // TMEM: kAccBufs x 2 accumulators x BN columns <= 512
+  static constexpr int kTmemCols = kAccBufs * 2 * BN;
+  static constexpr int kStoreBytes = 8 * 32 * 128;
   static constexpr int kSmemBytes = kAStages * kABytes + kBStages * kBBytes + kStoreBytes + 1024 + 512;
 };
 
-// K-major descriptor whose start is `row` rows (128 bytes each) and `kk` 16-element steps into a 1024-byte-aligned,
-// 128-byte-swizzled tile.  The tensor core applies the swizzle to the bits of the absolute shared-memory address, as
-// TMA did when it wrote the tile, so a start that is not 1024-byte aligned needs nothing more than its address (the
-// descriptor's base-offset field stays 0; setting it to the start's phase gives wrong products - measured).
-__device__ __forceinline__ uint64_t desc_k_major_at(uint32_t tile_addr, int row, int kk) {
-  return desc_k_major(tile_addr + (uint32_t)row * 128u + (uint32_t)kk * 32u);
-}
-
+// The operand of tap (kh, kw) is the bordered box read from row tap_off = kh * pitch + kw on: a start address that is
+// not 1024-byte aligned.  The tensor core applies the 128-byte swizzle to the bits of the absolute shared-memory
+// address, as TMA did when it wrote the tile, so the shifted start needs nothing beyond its address (the descriptor's
+// base-offset field stays 0; setting it to the start's phase gives wrong products - measured).
+// One tile = a bordered box of up to 256 accumulator rows (two 128-row accumulators that share every weight tile).
+// g.b_resident: all weight tiles of the problem (9 taps, one channel block, one N tile) fit the weight ring; they are
+// loaded once and stay.
 template <int BN, bool B_MN, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap wmap,
@@ -373,6 +419,8 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   const int tiles_m = g.tiles_w * g.tiles_h * g.tiles_n, tiles_nn = (g.nc + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_nn;
   const int kcb = g.kc >> 6;
+  const int n_sub = (g.pix + 127) >> 7;
+  const bool resident = g.b_resident != 0;
 
   // Rows of an A stage past the bordered box are never written by TMA but are read for accumulator rows that are
   // thrown away; they are zeroed once so that those rows stay finite.
@@ -384,7 +432,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kAStages; ++s) { mbar_init(a_full + s, 1); mbar_init(a_empty + s, 1); }
     for (int s = 0; s < C::kBStages; ++s) { mbar_init(b_full + s, 1); mbar_init(b_empty + s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar + a, 1); mbar_init(tmem_empty_bar + a, 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tmem_full_bar + a, 1); mbar_init(tmem_empty_bar + a, 8); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&amap) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&wmap) : "memory");
@@ -399,7 +447,7 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int t_first = tile_begin(num_tiles, blockIdx.x), my_tiles = tile_begin(num_tiles, blockIdx.x + 1) - t_first;
 
   if (warp == 0) {
     // ---------------- TMA producer: one bordered box per (tile, channel block), nine weight tiles after it; the box
@@ -409,12 +457,12 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
       uint32_t ib = 0;
       bool ok = true;
       auto load_a = [&](int u) -> bool {
-        const int t = blockIdx.x + (u / kcb) * gridDim.x, cb = u % kcb;
+        const int t = t_first + u / kcb, cb = u % kcb;
         int w0, h0, n0;
         tile_origin(g, t % tiles_m, w0, h0, n0);
         const int s = u % C::kAStages;
         const uint32_t round = (uint32_t)u / C::kAStages;
-        if (round > 0 && !mbar_wait(a_empty + s, (round - 1) & 1, status, 1, g.wait_ns)) return false;
+        if (round > 0 && !mbar_wait_parked(a_empty + s, (round - 1) & 1, status, 1, g.wait_ns)) return false;
         mbar_expect_tx(a_full + s, (uint32_t)g.halo_rows * 128u);
         tma_load_4d(a_tiles + s * C::kABytes, &amap, a_full + s, cb * 64, w0 - 1, h0 - 1, n0);
         return true;
@@ -422,12 +470,15 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
       if (units > 0) ok = load_a(0);
       for (int u = 0; u < units && ok; ++u) {
         if (u + 1 < units && !load_a(u + 1)) { ok = false; break; }
-        const int t = blockIdx.x + (u / kcb) * gridDim.x, cb = u % kcb;
+        if (resident && u > 0) continue;
+        const int t = t_first + u / kcb, cb = u % kcb;
         const int c0 = (t / tiles_m) * BN;
         for (int tap = 0; tap < 9; ++tap, ++ib) {
           const int s = ib % C::kBStages;
-          const uint32_t round = ib / C::kBStages;
-          if (round > 0 && !mbar_wait(b_empty + s, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+          if (ib % C::kBGroup == 0) {
+            const uint32_t grp = (ib / C::kBGroup) % C::kBGroups, round = (ib / C::kBGroup) / C::kBGroups;
+            if (round > 0 && !mbar_wait_parked(b_empty + grp, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+          }
           uint8_t* b_dst = b_tiles + s * C::kBBytes;
           mbar_expect_tx(b_full + s, (uint32_t)C::kBBytes);
           if constexpr (!B_MN) {
@@ -444,35 +495,44 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(128, BN, false, B_MN);
+      const uint32_t a_addr0 = smem_u32(a_tiles), b_addr0 = smem_u32(b_tiles);
       uint32_t ia = 0, ib = 0;
       bool ok = true;
       for (int lt = 0; lt < my_tiles && ok; ++lt) {
-        const uint32_t acc = lt & 1, use = (uint32_t)lt >> 1;
+        const uint32_t acc = (uint32_t)lt % C::kAccBufs, use = (uint32_t)lt / C::kAccBufs;
         if (use > 0) {
           ok = mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4, g.wait_ns);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * 2 * BN;
+        uint32_t accum = 0u;
         for (int cb = 0; cb < kcb && ok; ++cb, ++ia) {
           const int sa = ia % C::kAStages;
           ok = mbar_wait(a_full + sa, (ia / C::kAStages) & 1, status, 2, g.wait_ns);
           if (!ok) break;
-          const uint32_t a_addr = smem_u32(a_tiles + sa * C::kABytes);
+          const uint32_t a_lo0 = desc_lo_k_major(a_addr0 + sa * C::kABytes);
           for (int tap = 0; tap < 9; ++tap, ++ib) {
-            const int sb = ib % C::kBStages;
-            ok = mbar_wait(b_full + sb, (ib / C::kBStages) & 1, status, 2, g.wait_ns);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t b_addr = smem_u32(b_tiles + sb * C::kBBytes);
-            const int row = g.tap_off[tap];
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t b_desc = B_MN ? desc_mn_major(b_addr + kk * 2048, 8192) : desc_k_major(b_addr) + (uint64_t)(2 * kk);
-              umma_bf16(d_tmem, desc_k_major_at(a_addr, row, kk), b_desc, idesc,
-                        (cb > 0 || tap > 0 || kk > 0) ? 1u : 0u);
+            const int sb = resident ? tap : (int)(ib % C::kBStages);
+            if (!resident || ia == 0) {
+              ok = mbar_wait(b_full + sb, resident ? 0u : ((ib / C::kBStages) & 1), status, 2, g.wait_ns);
+              if (!ok) break;
             }
-            umma_commit(b_empty + sb);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t b_addr = b_addr0 + sb * C::kBBytes;
+            const uint32_t b_lo = B_MN ? desc_lo_mn_major(b_addr, 8192) : desc_lo_k_major(b_addr);
+            const uint32_t a_lo = a_lo0 + 8 * g.tap_off[tap];        // one row = 128 bytes = 8 address units
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_bf16_lo(d_tmem, a_lo + 2 * kk, b_lo + (B_MN ? 128 * kk : 2 * kk), idesc, kk == 0 ? accum : 1u);
+            if (n_sub > 1) {
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)                         // second accumulator: 128 rows further on
+                umma_bf16_lo(d_tmem + BN, a_lo + 1024 + 2 * kk, b_lo + (B_MN ? 128 * kk : 2 * kk), idesc,
+                             kk == 0 ? accum : 1u);
+            }
+            accum = 1u;
+            if (!resident && ib % C::kBGroup == C::kBGroup - 1) umma_commit(b_empty + (ib / C::kBGroup) % C::kBGroups);
           }
           if (ok) umma_commit(a_empty + sa);
         }
@@ -480,8 +540,8 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
       }
     }
   } else {
-    fwd_epilogue<BN, STATS>(g, num_tiles, tiles_m, tmem_base, tmem_full_bar, tmem_empty_bar, store_bufs, out, col_sums,
-                            status, warp, lane);
+    fwd_epilogue<BN, 2, C::kAccBufs, STATS>(g, num_tiles, tiles_m, n_sub, tmem_base, tmem_full_bar, tmem_empty_bar,
+                                            store_bufs, out, col_sums, status, warp, lane);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -507,7 +567,7 @@ struct WgCfg {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kWgThreads, 1)
 conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__ CUtensorMap dymap,
                   const __grid_constant__ Geom g, float* __restrict__ dw, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -533,7 +593,7 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
   {
     uint4* p = reinterpret_cast<uint4*>(tiles);
     const int n16 = C::kStages * C::kStageBytes / 16;
-    for (int i = threadIdx.x; i < n16; i += kThreads) p[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < n16; i += kWgThreads) p[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (threadIdx.x == 0) {
@@ -576,7 +636,7 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
           tile_origin(g, bx, w0, h0, n0);
           const int s = it % C::kStages;
           const uint32_t round = it / C::kStages;
-          if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+          if (round > 0 && !mbar_wait_parked(empty_bar + s, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
           uint8_t* a_dst = tiles + s * C::kStageBytes;
           uint8_t* b_dst = a_dst + C::kABytes;
           mbar_expect_tx(full_bar + s, tx);
@@ -596,6 +656,7 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(128, BN, true, true);
+      const uint32_t tiles_addr = smem_u32(tiles);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++lt) {
@@ -608,17 +669,19 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accum = 0u;
         for (int bx = b_lo; bx < b_hi; ++bx, ++it) {
           const int s = it % C::kStages;
           const uint32_t round = it / C::kStages;
           ok = mbar_wait(full_bar + s, round & 1, status, 2, g.wait_ns);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + s * C::kStageBytes);
-          const uint32_t b_addr = a_addr + C::kABytes;
-          for (int ks = 0; ks < ksteps; ++ks)
-            umma_bf16(d_tmem, desc_mn_major(a_addr + ks * 2048, C::kBox), desc_mn_major(b_addr + ks * 2048, C::kBox),
-                      idesc, (bx > b_lo || ks > 0) ? 1u : 0u);
+          const uint32_t a_addr = tiles_addr + s * C::kStageBytes;
+          const uint32_t a_dlo = desc_lo_mn_major(a_addr, C::kBox), b_dlo = desc_lo_mn_major(a_addr + C::kABytes, C::kBox);
+          for (int ks = 0; ks < ksteps; ++ks) {                     // 16 pixels further on: +2048 bytes
+            umma_bf16_lo(d_tmem, a_dlo + 128 * ks, b_dlo + 128 * ks, idesc, accum);
+            accum = 1u;
+          }
           umma_commit(empty_bar + s);
         }
         umma_commit(tmem_full_bar + acc);
@@ -633,7 +696,7 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
       const int mt = item % m_tiles, nt = (item / m_tiles) % n_tiles, sp = item / (m_tiles * n_tiles);
       const int b_lo = (int)((int64_t)boxes * sp / g.splits), b_hi = (int)((int64_t)boxes * (sp + 1) / g.splits);
       const uint32_t acc = lt & 1, use = lt >> 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3, g.wait_ns));
+      ok = mbar_wait_warp(tmem_full_bar + acc, use & 1, status, 3, g.wait_ns, lane);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = mt * 128 + quarter * 32 + lane;             // index into the (tap, ci) axis
@@ -795,11 +858,20 @@ int launch_fwd(const Plan& p, const CUtensorMap& wmap, void* out, float* col_sum
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  const Geom& g = p.g;
+  Geom g = p.g;
   const int num_tiles = g.tiles_w * g.tiles_h * g.tiles_n * ((g.nc + BN - 1) / BN);
   const int n_sm = sm_count();
   const int grid = num_tiles < n_sm ? num_tiles : n_sm;
-  kern<<<grid, kThreads, FwdCfg<BN>::kSmemBytes, stream>>>(p.maps, wmap, g, (__nv_bfloat16*)out, col_sums, status);
+  // flat pixel grid (1x1 stride 1, dense output rows): [pixels, nc] matrix written in 32-row x 64-channel TMA stores
+  CUtensorMap omap = wmap;
+  g.tma_store = 0;
+  if (g.out_h == 1 && g.out_n == 1 && g.out_sw * 8 == g.nc && g.box_w == 128) {
+    const uint64_t dims[2] = {(uint64_t)g.nc, (uint64_t)g.out_w};
+    const uint64_t strides[2] = {2, (uint64_t)g.nc * 2};
+    const uint32_t box[2] = {64, 32};
+    if (make_bf16_map(&omap, out, 2, dims, strides, box)) g.tma_store = 1;
+  }
+  kern<<<grid, kThreads, FwdCfg<BN>::kSmemBytes, stream>>>(p.maps, wmap, omap, g, (__nv_bfloat16*)out, col_sums, status);
   return TSP_LAUNCH_CHECK();
 }
 
@@ -825,7 +897,7 @@ bool halo_applies(int k, int s, int w, int h) {
 // Geometry of the halo kernel over src[n, h, w, c] (the forward's input, or dy for the data gradient).
 bool plan_halo(Geom& g, CUtensorMap* amap, const void* src, int n, int h, int w, int c) {
   g = Geom{};
-  const int pitch = w + 2, hmax = 128 / pitch;
+  const int pitch = w + 2, hmax = 256 / pitch;        // up to 256 accumulator rows (two accumulators) per tile
   const int th = (h + hmax - 1) / hmax;
   g.out_w = w; g.out_h = h; g.out_n = n;
   g.box_w = w; g.box_h = (h + th - 1) / th; g.box_n = 1;
@@ -861,8 +933,9 @@ int launch_halo(const Geom& g, const CUtensorMap& amap, const CUtensorMap& wmap,
 }
 
 template <bool B_MN, bool STATS>
-int dispatch_halo(int bn, const Geom& g, const CUtensorMap& amap, const CUtensorMap& wmap, void* out, float* col_sums,
+int dispatch_halo(int bn, Geom& g, const CUtensorMap& amap, const CUtensorMap& wmap, void* out, float* col_sums,
                   int* status, cudaStream_t stream) {
+  g.b_resident = (bn == 64 && g.kc == 64 && g.nc == 64) ? 1 : 0;      // 9 weight tiles = the 9 ring slots
   if (bn == 256) return launch_halo<256, B_MN, STATS>(g, amap, wmap, out, col_sums, status, stream);
   if (bn == 128) return launch_halo<128, B_MN, STATS>(g, amap, wmap, out, col_sums, status, stream);
   return launch_halo<64, B_MN, STATS>(g, amap, wmap, out, col_sums, status, stream);
@@ -887,7 +960,7 @@ int launch_wgrad(const Plan& p, const CUtensorMap& dymap, float* dw, int* status
   const int items = m_tiles * n_tiles * g.splits;
   const int n_sm = sm_count();
   const int grid = items < n_sm ? items : n_sm;
-  kern<<<grid, kThreads, WgCfg<BN>::kSmemBytes, stream>>>(p.maps, dymap, g, dw, status);
+  kern<<<grid, kWgThreads, WgCfg<BN>::kSmemBytes, stream>>>(p.maps, dymap, g, dw, status);
   return TSP_LAUNCH_CHECK();
 }
 

@@ -59,6 +59,64 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
+// Wait of a role that is not on the critical path (epilogue warps, the TMA producer): mbarrier.try_wait with a long
+// suspend-time hint parks the thread until the phase completes or the hint expires, so a waiting warp issues a few
+// instructions per microsecond instead of competing with the MMA-issuing thread on its scheduler.
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                 uint64_t limit_ns) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t t0 = 0;
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      uint32_t done;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+          "selp.b32 %0, 1, 0, p;\n\t}"
+          : "=r"(done)
+          : "r"(addr), "r"(parity), "r"(2000u)
+          : "memory");
+      if (done) return true;
+    }
+    if (*((volatile int*)status) != 0) return false;
+    const uint64_t now = global_timer_ns();
+    if (t0 == 0) t0 = now;
+    else if (now - t0 > limit_ns) break;
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+// The same for a whole warp: lane 0 waits, the others park at the warp barrier; every lane gets the result.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code, uint64_t limit_ns,
+                                               int lane) {
+  int ok = 0;
+  if (lane == 0) ok = mbar_wait_parked(bar, parity, status, code, limit_ns) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// The MMA-issuing thread is the one serial resource of these kernels (an issue costs it about 50 cycles), so its loop
+// works on 32-bit halves of the matrix descriptors: the high word (stride byte offset 1024, version, 128-byte swizzle)
+// is the same constant for K-major and MN-major tiles, the low word is (address >> 4) plus the leading-byte-offset
+// field, and stepping through a tile only ever adds to the low word (shared-memory addresses stay below 2^18, so the
+// 14-bit address field cannot carry).
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_k_major(uint32_t smem_addr) { return (smem_addr >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mn_major(uint32_t smem_addr, uint32_t lbo) {
+  return (smem_addr >> 4) | ((lbo >> 4) << 16);
+}
+__device__ __forceinline__ void umma_bf16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -71,6 +129,15 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+
+// TMA store of one 32-row x 128-byte block (128-byte swizzle) from shared memory; rows / columns beyond the
+// tensor's extent are clipped by the hardware.  x must be a multiple of 8 elements (16 bytes).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
 // K-major operand tile [rows][64 bf16 = 128 bytes], 128-byte swizzle, 8-row groups 1024 bytes apart.  Advancing 16
