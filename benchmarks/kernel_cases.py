@@ -7,7 +7,7 @@
     python benchmarks/kernel_cases.py ema       # momentum-teacher update over 25 M parameters
     python benchmarks/kernel_cases.py kd        # soft-target KD loss on [2048, 1000] logits
     python benchmarks/kernel_cases.py ln        # LayerNorm fwd/bwd on [512*197, 768]
-    python benchmarks/kernel_cases.py gemm      # tcgen05 GEMM 8192 x 3072 x 768
+    python benchmarks/kernel_cases.py gemm [M N K]   # tcgen05 GEMM (default 8192 x 3072 x 768)
     python benchmarks/kernel_cases.py infonce   # MoCo InfoNCE forward + backward, 4096 x 256
     python benchmarks/kernel_cases.py attn      # ViT-B attention forward (tcgen05 flash-style kernel)
     python benchmarks/kernel_cases.py conv [N]  # every 1x1 / 3x3 convolution shape of ResNet-50 (batch N, default 256):
@@ -187,16 +187,18 @@ def case_ln():
 def case_gemm():
     from tspipe_b200.ops import gemm
     dev = torch.device("cuda")
-    m, n, k = 8192, 3072, 768
+    m, n, k = (int(v) for v in sys.argv[2:5]) if len(sys.argv) > 4 else (8192, 3072, 768)
     a = torch.randn(m, k, device=dev).bfloat16()
     b = torch.randn(n, k, device=dev).bfloat16()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bias = torch.randn(n, device=dev)
     t2 = _time(lambda: gemm.matmul_nt(a, b, two_cta=True), n=10, flush=flush)
+    t2b = _time(lambda: gemm.matmul_nt(a, b, bias, two_cta=True), n=10, flush=flush)
     t1 = _time(lambda: gemm.matmul_nt(a, b, two_cta=False), n=10, flush=flush)
     tr = _time(lambda: a @ b.t(), n=10, flush=flush)
     gemm.check_status()
     f = 2 * m * n * k / 1e6
-    print(f"tcgen05 gemm {m}x{n}x{k}: CTA pair {t2:7.1f} us {f / t2:7.1f} TFLOP/s | one CTA {t1:7.1f} us {f / t1:7.1f} TFLOP/s"
+    print(f"tcgen05 gemm {m}x{n}x{k}: CTA pair {t2:7.1f} us {f / t2:7.1f} TFLOP/s (with bias {t2b:7.1f} us) | one CTA {t1:7.1f} us {f / t1:7.1f} TFLOP/s"
           f" | library {tr:7.1f} us {f / tr:7.1f} TFLOP/s")
 
 

@@ -65,6 +65,7 @@ struct Geom {
   int halo_rows;                            // halo kernel: (box_w + 2) * (box_h + 2) rows fetched per channel block
   int b_resident;                           // halo kernel: the nine weight tiles are loaded once and stay
   int tma_store;                            // forward kernel, flat pixel grid: the epilogue writes with TMA stores
+  int n_fastest;                            // tile index = m_tile * tiles_n + n_tile (else n_tile * tiles_m + m_tile)
   unsigned long long wait_ns;               // give-up time of every mbarrier wait
   int n_taps;
   int kc;                                   // channels per tap on the contraction side (forward) / on the M side (wgrad)
@@ -98,6 +99,14 @@ struct FwdCfg {
 // and consecutive tiles are neighbouring pixel boxes.
 __device__ __forceinline__ int tile_begin(int num_tiles, unsigned cta) {
   return (int)((long long)num_tiles * cta / gridDim.x);
+}
+
+// Split a tile index into (pixel tile, channel tile).  With statistics a CTA should stay on one channel block (one set
+// of accumulators, few flushes): channel-major.  Without, channel tiles run fastest: the CTAs that run together share
+// a pixel tile's input (fetched from DRAM once, then from L2) and sweep the weights, which stay in L2.
+__device__ __forceinline__ void split_tile(const Geom& g, int t, int tiles_m, int tiles_nn, int& tm, int& tn) {
+  if (g.n_fastest) { tm = t / tiles_nn; tn = t % tiles_nn; }
+  else { tm = t % tiles_m; tn = t / tiles_m; }
 }
 
 __device__ __forceinline__ void tile_origin(const Geom& g, int tm, int& w0, int& h0, int& n0) {
@@ -147,9 +156,10 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
   };
   const int t_begin = tile_begin(num_tiles, blockIdx.x), t_end = tile_begin(num_tiles, blockIdx.x + 1);
   for (int t = t_begin; t < t_end && ok; ++t, ++lt) {
-    int w0, h0, n0;
-    tile_origin(g, t % tiles_m, w0, h0, n0);
-    const int c0 = (t / tiles_m) * BN;
+    int w0, h0, n0, tm, tn;
+    split_tile(g, t, tiles_m, (g.nc + BN - 1) / BN, tm, tn);
+    tile_origin(g, tm, w0, h0, n0);
+    const int c0 = tn * BN;
     const uint32_t acc = lt % ACC_BUFS, use = lt / ACC_BUFS;
     if (STATS) {
       const int seg = (int)((((int64_t)n0 * g.out_h + h0) * g.out_w + w0) / g.rows_per_seg);
@@ -297,9 +307,10 @@ conv_fwd_kernel(const __grid_constant__ ActMaps amaps, const __grid_constant__ C
       bool ok = true;
       const uint32_t tx = (uint32_t)(g.pix * 128 + C::kBBytes);     // a box is written in full, zero fill included
       for (int t = tile_begin(num_tiles, blockIdx.x); t < tile_begin(num_tiles, blockIdx.x + 1) && ok; ++t) {
-        int w0, h0, n0;
-        tile_origin(g, t % tiles_m, w0, h0, n0);
-        const int c0 = (t / tiles_m) * BN;
+        int w0, h0, n0, tm, tn;
+        split_tile(g, t, tiles_m, tiles_nn, tm, tn);
+        tile_origin(g, tm, w0, h0, n0);
+        const int c0 = tn * BN;
         for (int tap = 0; tap < g.n_taps && ok; ++tap) {
           const CUtensorMap* am = &amaps.m[g.tap_map[tap]];
           const int xw = w0 + g.tap_dw[tap], xh = h0 + g.tap_dh[tap], wcol = g.tap_col[tap];
@@ -458,8 +469,9 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
       bool ok = true;
       auto load_a = [&](int u) -> bool {
         const int t = t_first + u / kcb, cb = u % kcb;
-        int w0, h0, n0;
-        tile_origin(g, t % tiles_m, w0, h0, n0);
+        int w0, h0, n0, tm, tn;
+        split_tile(g, t, tiles_m, tiles_nn, tm, tn);
+        tile_origin(g, tm, w0, h0, n0);
         const int s = u % C::kAStages;
         const uint32_t round = (uint32_t)u / C::kAStages;
         if (round > 0 && !mbar_wait_parked(a_empty + s, (round - 1) & 1, status, 1, g.wait_ns)) return false;
@@ -472,7 +484,9 @@ conv_halo_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant
         if (u + 1 < units && !load_a(u + 1)) { ok = false; break; }
         if (resident && u > 0) continue;
         const int t = t_first + u / kcb, cb = u % kcb;
-        const int c0 = (t / tiles_m) * BN;
+        int tm, tn;
+        split_tile(g, t, tiles_m, tiles_nn, tm, tn);
+        const int c0 = tn * BN;
         for (int tap = 0; tap < 9; ++tap, ++ib) {
           const int s = ib % C::kBStages;
           if (ib % C::kBGroup == 0) {
@@ -562,6 +576,8 @@ struct WgCfg {
   static constexpr int kBBytes = (BN / 64) * kBox;              // BN / 64 boxes of dY
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 128 ? 3 : 4;
+  static constexpr int kGroup = BN == 128 ? 1 : 2;              // stages released per tcgen05.commit
+  static constexpr int kGroups = kStages / kGroup;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 };
@@ -635,8 +651,10 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
           int w0, h0, n0;
           tile_origin(g, bx, w0, h0, n0);
           const int s = it % C::kStages;
-          const uint32_t round = it / C::kStages;
-          if (round > 0 && !mbar_wait_parked(empty_bar + s, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+          if (it % C::kGroup == 0) {
+            const uint32_t grp = (it / C::kGroup) % C::kGroups, round = (it / C::kGroup) / C::kGroups;
+            if (round > 0 && !mbar_wait_parked(empty_bar + grp, (round - 1) & 1, status, 1, g.wait_ns)) { ok = false; break; }
+          }
           uint8_t* a_dst = tiles + s * C::kStageBytes;
           uint8_t* b_dst = a_dst + C::kABytes;
           mbar_expect_tx(full_bar + s, tx);
@@ -682,7 +700,7 @@ conv_wgrad_kernel(const __grid_constant__ ActMaps xmaps, const __grid_constant__
             umma_bf16_lo(d_tmem, a_dlo + 128 * ks, b_dlo + 128 * ks, idesc, accum);
             accum = 1u;
           }
-          umma_commit(empty_bar + s);
+          if (it % C::kGroup == C::kGroup - 1) umma_commit(empty_bar + (it / C::kGroup) % C::kGroups);
         }
         umma_commit(tmem_full_bar + acc);
       }
@@ -865,6 +883,7 @@ int launch_fwd(const Plan& p, const CUtensorMap& wmap, void* out, float* col_sum
   // flat pixel grid (1x1 stride 1, dense output rows): [pixels, nc] matrix written in 32-row x 64-channel TMA stores
   CUtensorMap omap = wmap;
   g.tma_store = 0;
+  g.n_fastest = STATS ? 0 : 1;
   if (g.out_h == 1 && g.out_n == 1 && g.out_sw * 8 == g.nc && g.box_w == 128) {
     const uint64_t dims[2] = {(uint64_t)g.nc, (uint64_t)g.out_w};
     const uint64_t strides[2] = {2, (uint64_t)g.nc * 2};
@@ -913,8 +932,9 @@ bool plan_halo(Geom& g, CUtensorMap* amap, const void* src, int n, int h, int w,
 }
 
 template <int BN, bool B_MN, bool STATS>
-int launch_halo(const Geom& g, const CUtensorMap& amap, const CUtensorMap& wmap, void* out, float* col_sums, int* status,
+int launch_halo(Geom& g, const CUtensorMap& amap, const CUtensorMap& wmap, void* out, float* col_sums, int* status,
                 cudaStream_t stream) {
+  g.n_fastest = STATS ? 0 : 1;
   auto kern = conv_halo_kernel<BN, B_MN, STATS>;
   static bool attr_set[64] = {};
   int dev = 0;

@@ -6,11 +6,13 @@
 // CTA's 128 x 256 accumulator slice into that CTA's tensor memory.  Compared with the one-CTA kernel
 // (gemm_tcgen05.cu: 48 KB of operands per 128 x 256 x 64 step) each SM moves 32 KB per step for the same FLOPs.
 //
-// Synchronisation (all mbarriers; every wait bounded, see mbar_wait):
+// Synchronisation (all mbarriers; every wait bounded in time, see tc5::mbar_wait):
 //   full[s]        in the leader: armed by the leader's producer with the bytes of BOTH CTAs; every TMA load of the
 //                  pair completes its bytes on the leader's barrier (cp.async.bulk.tensor ... .cta_group::2);
-//   empty[s]       in each CTA: the leader commits the MMAs that read slot s to its own and to the peer's barrier;
-//   tmem_full[a]   in each CTA: committed by the leader after the last MMA of a tile;
+//   empty[g]       in each CTA, one per GROUP of two slots: after the MMAs of a group's second slot the leader issues
+//                  ONE tcgen05.commit that arrives on the barrier of both CTAs (a commit costs the issuing thread as
+//                  much as eight MMA issues; two per k-block made the issuing thread, not the tensor core, the limit);
+//   tmem_full[a]   in each CTA: committed by the leader (to both CTAs at once) after the last MMA of a tile;
 //   tmem_empty[a]  in the leader: 8 arrivals, one per epilogue warp of the pair (the peer's arrive remotely).
 // Epilogue: TMEM -> registers -> swizzled shared memory -> TMA store (32 rows x 128 bytes per store, two buffers
 // per warp); direct per-thread stores when C has no 16-byte-aligned base and row pitch.
@@ -18,7 +20,7 @@
 // partner can still touch its shared memory.
 #include <cuda.h>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 #include "tspipe_kernels.h"
 
 namespace {
@@ -29,7 +31,9 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kStages = 6;
 constexpr int kThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint64_t kWaitNs = 2000000000ull;   // every mbarrier wait gives up after two seconds
+constexpr int kGroup = 2;                       // stages released per tcgen05.commit
+constexpr int kGroups = kStages / kGroup;
 constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = (BN / 2) * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;                  // per CTA
@@ -63,27 +67,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-    // The error word lives in global memory, so this check costs a round trip to L2 per failed poll.  That is
-    // deliberate: it is the back-off of the spin loop.  Polling the barrier flat out was measured slower (the
-    // waiting warps take issue slots from the one thread that feeds the pipeline).
-    if (*((volatile int*)status) != 0) return false;
-  }
-  atomicCAS(status, 0, code);
-  return false;
-}
-
 // TMA load into this CTA's shared memory whose byte count completes on a barrier of the pair's leader.
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int x,
                                                  int y) {
@@ -94,31 +77,26 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       : "memory");
 }
 
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;          // SWIZZLE_128B
-  return d;
-}
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                               uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// arrive on a barrier (any CTA of the cluster) once all MMAs issued so far by this thread have completed
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+// one commit that arrives on the barrier at the same shared-memory offset in BOTH CTAs of the pair (a commit costs
+// the issuing thread about as much as eight MMA issues, so the pair is signalled with one instruction, not two)
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t local_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(local_bar_addr), "h"((uint16_t)3)
                : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(tc5::kDescHi), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 __device__ __forceinline__ void tmem_ld_32x32_issue(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -204,12 +182,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t it = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM;
-        const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
+        // N tiles fastest: the pairs that run together share rows of A (read from DRAM once, then from L2) and sweep
+        // the weights, which stay in L2; walking all of M per N tile would stream A from DRAM once per N tile
+        const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM;
+        const int n0 = (t % tiles_n) * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
-          const uint32_t round = it / kStages;
-          if (round > 0 && !mbar_wait(empty_bar + s, (round - 1) & 1, status, 1)) { ok = false; break; }
+          if (it % kGroup == 0) {                 // first stage of a group: the whole group must have been released
+            const uint32_t grp = (it / kGroup) % kGroups, round = (it / kGroup) / kGroups;
+            if (round > 0 && !tc5::mbar_wait_parked(empty_bar + grp, (round - 1) & 1, status, 1, kWaitNs)) { ok = false; break; }
+          }
           uint8_t* a_dst = tiles + s * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           if (leader) mbar_expect_tx(full_bar + s, 2u * (uint32_t)kStageBytes);
@@ -223,35 +205,35 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      const uint32_t tiles_addr = smem_u32(tiles);
       uint32_t it = 0, lt = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
         const uint32_t acc = lt & 1, use = lt >> 1;
         if (use > 0) {
-          ok = mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4);
+          ok = tc5::mbar_wait(tmem_empty_bar + acc, (use - 1) & 1, status, 4, kWaitNs);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accum = 0u;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t round = it / kStages;
-          ok = mbar_wait(full_bar + s, round & 1, status, 2);
+          ok = tc5::mbar_wait(full_bar + s, round & 1, status, 2, kWaitNs);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = smem_u32(tiles + s * kStageBytes);
-          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kABytes);
+          const uint32_t a_addr = tiles_addr + s * kStageBytes;
+          const uint32_t a_lo = tc5::desc_lo_k_major(a_addr), b_lo = tc5::desc_lo_k_major(a_addr + kABytes);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_bf16_pair(d_tmem, a_desc + (uint64_t)(2 * kk), b_desc + (uint64_t)(2 * kk), idesc,
-                           (kb > 0 || kk > 0) ? 1u : 0u);
-          const uint32_t e_local = smem_u32(empty_bar + s);
-          umma_commit_pair(e_local);                       // slot s is free again in this CTA ...
-          umma_commit_pair(map_to_cta(e_local, 1));        // ... and in the partner
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            umma_bf16_pair_lo(d_tmem, a_lo + 2 * kk, b_lo + 2 * kk, idesc, accum);
+            accum = 1u;
+          }
+          // the group's slots are free again in both CTAs once these MMAs have read them
+          if (it % kGroup == kGroup - 1) umma_commit_pair_both(smem_u32(empty_bar + (it / kGroup) % kGroups));
         }
-        const uint32_t f_local = smem_u32(tmem_full_bar + acc);
-        umma_commit_pair(f_local);
-        umma_commit_pair(map_to_cta(f_local, 1));
+        umma_commit_pair_both(smem_u32(tmem_full_bar + acc));
       }
     }
   } else {
@@ -285,13 +267,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
     };
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
-      const int m0 = (t % tiles_m) * 2 * BM + (int)rank * BM, n0 = (t / tiles_m) * BN;
+      const int m0 = (t / tiles_n) * 2 * BM + (int)rank * BM, n0 = (t % tiles_n) * BN;
       const uint32_t acc = lt & 1, use = lt >> 1;
       if (STATS) {
         const int seg = m0 / seg_rows;
         if (n0 != cur_n0 || seg != cur_seg) { flush_stats(); cur_n0 = n0; cur_seg = seg; }
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar + acc, use & 1, status, 3));   // one way out per warp
+      ok = tc5::mbar_wait_warp(tmem_full_bar + acc, use & 1, status, 3, kWaitNs, lane);   // one way out per warp
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row0 = m0 + quarter * 32, row = row0 + lane;
@@ -310,10 +292,22 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         const int col = n0 + c0;
         if (epi != 0 && col < n) {
+          if (col + kCols <= n && (((uintptr_t)(bias + col)) & 15) == 0) {
+            // whole block inside the matrix: the block's bias values as 16-byte loads (every lane reads the same
+            // addresses, one broadcast transaction each) instead of one scalar load per element
+            const float4* bp = reinterpret_cast<const float4*>(bias + col);
 #pragma unroll
-          for (int j = 0; j < kCols; ++j) {
-            v[j] += (col + j < n) ? bias[col + j] : 0.f;
-            if (epi == 2) v[j] = gelu_erf(v[j]);
+            for (int j = 0; j < kCols / 4; ++j) {
+              const float4 b4 = __ldg(bp + j);
+              v[4 * j + 0] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) v[j] += (col + j < n) ? bias[col + j] : 0.f;
+          }
+          if (epi == 2) {
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) v[j] = gelu_erf(v[j]);
           }
         }
         if (tma_store) {

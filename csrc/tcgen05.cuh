@@ -3,6 +3,7 @@
 // descriptor, MMA issue / commit, TMEM loads, and tensor-map encoding through the driver entry point.
 #pragma once
 #include <cuda.h>
+#include <dlfcn.h>
 
 #include "common.cuh"
 
@@ -213,8 +214,13 @@ inline EncodeTiledFn get_encode() {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
+        q == cudaDriverEntryPointSuccess && p != nullptr) {
       fn = (EncodeTiledFn)p;
+    } else {
+      (void)cudaGetLastError();               // the query failed (seen on a thread's first runtime call): ask the
+      void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);      // driver library itself
+      if (h != nullptr) fn = (EncodeTiledFn)dlsym(h, "cuTensorMapEncodeTiled");
+    }
   }
   return fn;
 }
@@ -229,9 +235,16 @@ inline bool make_bf16_map(CUtensorMap* map, const void* base, int rank, const ui
   cuuint32_t b[4], e[4];
   for (int i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; e[i] = 1; }
   for (int i = 1; i < rank; ++i) s[i - 1] = strides[i];
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  CUresult r = CUDA_ERROR_UNKNOWN;
+  for (int attempt = 0; attempt < 2 && r != CUDA_SUCCESS; ++attempt) {
+    // The encoder is a driver call and wants a current context.  A thread that has not made a runtime call yet (an
+    // autograd worker calling straight into this library) has none: bind the device's primary context and retry.
+    if (attempt == 1) (void)cudaFree(nullptr);
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r == CUDA_SUCCESS;
 }
 
 }  // namespace tc5

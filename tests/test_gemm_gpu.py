@@ -67,3 +67,36 @@ def test_linear_autograd_and_info_nce():
     ref.backward()
     torch.testing.assert_close(loss, ref.detach(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(q.grad, qr.grad, rtol=1e-1, atol=2e-4)
+
+
+@pytest.mark.parametrize("rows,k,n", [((4, 64), 128, 256), ((3, 197), 768, 2304), ((1000,), 64, 64), ((5, 130), 3072, 768)])
+def test_linear_forward_and_both_backward_products_on_tcgen05(rows, k, n):
+    """``ops.linear.linear`` under bf16 autocast (the default path of the transformer blocks and heads): output, dX,
+    dW (added in place into an existing fp32 gradient) and db against fp32 F.linear on the same bf16-rounded
+    operands; ragged row counts included."""
+    from tspipe_b200.ops import gemm
+    from tspipe_b200.ops.linear import linear
+    torch.manual_seed(5)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(*rows, k, device=dev, requires_grad=True)
+    w = (torch.randn(n, k, device=dev) * 0.05).requires_grad_()
+    bias = torch.randn(n, device=dev, requires_grad=True)
+    w.grad = torch.full_like(w, 0.5)                 # an existing gradient: the kernel accumulates into it
+    before = gemm._f.LAUNCHES
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        assert gemm.eligible(x, w)
+        y = linear(x, w, bias)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gemm.check_status()
+    assert gemm._f.LAUNCHES - before >= 3            # forward GEMM, dX, dW (+ bias gradient) are own launches
+    xr = x.detach().bfloat16().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    br = bias.detach().clone().requires_grad_()
+    yr = F.linear(xr, wr, br)
+    yr.backward(g.float())
+    scale = (k ** 0.5) / 8
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=0.05 * scale)
+    torch.testing.assert_close(x.grad, xr.grad, rtol=3e-2, atol=3e-2 * max(xr.grad.abs().max().item(), 1e-3))
+    torch.testing.assert_close(w.grad - 0.5, wr.grad, rtol=3e-2, atol=3e-2 * wr.grad.abs().max().item())
+    torch.testing.assert_close(bias.grad, br.grad, rtol=2e-2, atol=2e-2 * br.grad.abs().max().item())

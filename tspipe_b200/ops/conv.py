@@ -14,6 +14,7 @@ Reference call sites: the convolutions of the torchvision ResNet that
 from __future__ import annotations
 
 import ctypes as _c
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -99,8 +100,9 @@ def stem_conv(x: torch.Tensor, weight: torch.Tensor, want_sums: bool = True, seg
 # -------------------------------------------------------------------------------------------------
 # 1x1 / 3x3 convolutions: implicit GEMM on tcgen05 (csrc/conv_igemm_tcgen05.cu)
 # -------------------------------------------------------------------------------------------------
-_IGEMM = True        # eligible convolutions run on the tcgen05 implicit-GEMM kernels (set_igemm(False): library)
-_W16 = {}            # id(weight) -> (weight, bf16 [Cout, k, k, Cin] copy); dropped at every optimizer step
+# eligible convolutions run on the tcgen05 implicit-GEMM kernels (set_igemm(False) or TSPIPE_CONV=library: library)
+_IGEMM = os.environ.get("TSPIPE_CONV", "igemm") != "library"
+_W16 = {}            # id(weight) -> (weight, version, bf16 [Cout, k, k, Cin] copy); dropped at every optimizer step
 
 
 def set_igemm(flag: bool) -> None:
@@ -117,12 +119,12 @@ def _w16(weight: torch.Tensor) -> torch.Tensor:
     """bf16 copy of a convolution weight laid out ``[Cout][kh][kw][Cin]`` (no copy beyond the cast when the
     parameter is stored channels-last, which is how the runtime keeps 4-D parameters)."""
     hit = _W16.get(id(weight))
-    if hit is not None and hit[0] is weight and hit[1].device == weight.device:
-        return hit[1]
+    if hit is not None and hit[0] is weight and hit[1] == weight._version and hit[2].device == weight.device:
+        return hit[2]
     w = weight.detach().to(torch.bfloat16).permute(0, 2, 3, 1)
     if not w.is_contiguous():
         w = w.contiguous()
-    _W16[id(weight)] = (weight, w)
+    _W16[id(weight)] = (weight, weight._version, w)
     return w
 
 

@@ -2,8 +2,10 @@
 
 ``matmul_nt(a, b)`` computes ``a @ b.T`` for row-major bf16 ``a [M, K]`` and ``b [N, K]`` with fp32
 accumulation in tensor memory, optional fused ``+ bias`` and GELU epilogue.  ``linear`` is the autograd
-wrapper used by the transformer blocks (forward on the tcgen05 kernel; the two backward products need
-transposed operands and use the library GEMM).  ``info_nce`` is the MoCo-v3 contrastive loss
+wrapper used by the transformer blocks and heads: forward on the CTA-pair tcgen05 GEMM, ``dX = dY W`` and
+``dW = dY^T X`` on the implicit-GEMM kernels of ``csrc/conv_igemm_tcgen05.cu`` (a linear layer is a 1x1
+convolution over its rows: the weight is read in place as MN-major tiles, the weight gradient is added into
+the fp32 gradient buffer), the bias gradient on the streaming column-sum kernel.  ``info_nce`` is the MoCo-v3 contrastive loss
 (`benchmarks/moco-v3/main.py:147-162`): row-normalised ``q @ k.T / T`` on the tcgen05 kernel followed
 by the fused cross-entropy kernel (value + gradient in one launch).
 
@@ -41,9 +43,15 @@ def check_status(device=None) -> None:
 
 
 def eligible(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Shapes and dtypes the tcgen05 linear path takes: bf16 compute (a bf16 input, or bf16 autocast), feature counts
+    multiples of 64, at least one full tile of rows."""
     k = x.shape[-1]
-    return (x.is_cuda and weight.is_cuda and k % 8 == 0 and k >= 64 and weight.shape[0] >= 64
-            and x.numel() // k >= 128)
+    if not (x.is_cuda and weight.is_cuda and weight.dim() == 2):
+        return False
+    if not (x.dtype == torch.bfloat16 or (torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16)):
+        return False
+    return k % 64 == 0 and weight.shape[0] % 64 == 0 and x.numel() // k >= 128 and weight.stride(1) == 1 \
+        and weight.stride(0) == k
 
 
 _two_cta = True     # measured faster than the one-CTA kernel on every ViT / head shape tried
@@ -81,11 +89,75 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = N
     return c
 
 
+_W16 = {}        # id(parameter) -> (parameter, version, bf16 copy); dropped at every optimizer step
+
+
+def clear_weight_cache() -> None:
+    _W16.clear()
+    _W16T.clear()
+
+
+def _w16(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a weight matrix, cast once per parameter and optimizer step.  A row slice of a parameter (the q / k
+    / v blocks of a fused projection) maps to the same slice of the parameter's copy.  The cache entry holds the
+    parameter itself, so an address that is reused by another tensor can never alias an old entry."""
+    if weight.dtype == torch.bfloat16 and weight.is_contiguous():
+        return weight.detach()
+    base = weight._base if weight._base is not None else weight
+    if not base.is_contiguous() or base.dtype == torch.bfloat16:
+        return weight.detach().to(torch.bfloat16).contiguous()
+    hit = _W16.get(id(base))
+    if hit is None or hit[0] is not base or hit[1] != base._version:
+        hit = (base, base._version, base.detach().to(torch.bfloat16))
+        _W16[id(base)] = hit
+    b16 = hit[2]
+    if base is weight:
+        return b16
+    return b16.as_strided(weight.shape, weight.stride(), weight.storage_offset() - base.storage_offset())
+
+
+_W16T = {}       # id(parameter slice base) -> (weight, version, bf16 transposed copy [K, N])
+
+
+def _w16_t(weight: torch.Tensor) -> torch.Tensor:
+    """bf16 ``weight.T`` as a contiguous ``[K, N]`` matrix (the B operand of ``dX = dY @ W`` on the ``A @ B^T`` GEMM),
+    made once per weight and optimizer step."""
+    base = weight._base if weight._base is not None else weight
+    key = (id(base), weight.storage_offset(), tuple(weight.shape))
+    hit = _W16T.get(key)
+    if hit is None or hit[0] is not base or hit[1] != base._version:
+        hit = (base, base._version, _w16(weight).t().contiguous())
+        _W16T[key] = hit
+    return hit[2]
+
+
+def _column_sums(dy2: torch.Tensor) -> torch.Tensor:
+    """fp32 column sums of a bf16 matrix (the bias gradient) on the streaming statistics kernel."""
+    m, n = dy2.shape
+    if n % 8 or n > 4096 or m < 2:
+        return dy2.float().sum(0)
+    sums = torch.empty(2 * n, dtype=torch.float32, device=dy2.device)
+    L = _f.lib()
+    L.tsp_bn_stats.restype = _c.c_int
+    with torch.cuda.device(dy2.device):
+        _f._check(L.tsp_bn_stats(_f._ptr(dy2), _c.c_int64(m), _c.c_int(n), _c.c_int(_f._dt(dy2)), _f._ptr(sums),
+                                 _c.c_int(1), _f._stream()), "tsp_bn_stats")
+    _f._count(2)
+    return sums[:n]
+
+
+# dX = dY @ W: on the CTA-pair GEMM against a cached transposed bf16 copy of W (True), or on the implicit-GEMM
+# data-gradient kernel that reads W in place as MN-major tiles (False; no transposed copy, about half the speed)
+_DX_ON_PAIR_GEMM = True
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        y = matmul_nt(x2, weight, bias)
+        if x2.dtype != torch.bfloat16 or not x2.is_contiguous():
+            x2 = x2.to(torch.bfloat16).contiguous()
+        y = matmul_nt(x2, _w16(weight), bias)
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.in_shape = x.shape
@@ -94,11 +166,45 @@ class _Linear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
+        from . import conv as _conv
         x2, weight = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16)
-        dx = (dy2 @ weight.to(torch.bfloat16)).view(ctx.in_shape).to(ctx.dtypes[0])
-        dw = (dy2.t() @ x2.to(torch.bfloat16)).to(ctx.dtypes[1])
-        db = dy2.float().sum(0).to(ctx.dtypes[2]) if ctx.has_bias else None
+        m, k = x2.shape
+        n = weight.shape[0]
+        dy2 = dy.reshape(-1, n)
+        if dy2.dtype != torch.bfloat16 or not dy2.is_contiguous():
+            dy2 = dy2.to(torch.bfloat16).contiguous()
+        L = _conv._lib()
+        status = _f._ptr(_status_word(x2.device))
+        dims = (_c.c_int(m), _c.c_int(1), _c.c_int(1), _c.c_int(k), _c.c_int(n), _c.c_int(1), _c.c_int(1))
+        dx = dw = db = None
+        with torch.cuda.device(x2.device):
+            st = _f._stream()
+            if ctx.needs_input_grad[0]:
+                if _DX_ON_PAIR_GEMM:
+                    dx2 = matmul_nt(dy2, _w16_t(weight))          # dX = dY @ W on the CTA-pair GEMM
+                else:
+                    dx2 = torch.empty((m, k), dtype=torch.bfloat16, device=x2.device)
+                    _f._check(L.tsp_conv_dgrad(_f._ptr(dy2), _f._ptr(_w16(weight)), _f._ptr(dx2), *dims, status, st),
+                              "tsp_conv_dgrad")
+                    _f._count()
+                dx = dx2.view(ctx.in_shape)
+                if ctx.dtypes[0] != torch.bfloat16:
+                    dx = dx.to(ctx.dtypes[0])
+            if ctx.needs_input_grad[1]:
+                g = weight.grad
+                if (_conv._ACCUMULATE_IN_PLACE and g is not None and g.dtype == torch.float32 and g.is_contiguous()
+                        and g.shape == weight.shape):
+                    target = g                     # the kernel adds into the existing gradient buffer
+                else:
+                    target = torch.zeros((n, k), dtype=torch.float32, device=x2.device)
+                    dw = target if weight.dtype == torch.float32 else target.to(weight.dtype)
+                _f._check(L.tsp_conv_wgrad(_f._ptr(x2), _f._ptr(dy2), _f._ptr(target), *dims, status, st),
+                          "tsp_conv_wgrad")
+                _f._count()
+                if dw is not None and dw is not target:
+                    dw = target.to(weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _column_sums(dy2).to(ctx.dtypes[2])
         return dx, dw, db
 
 

@@ -1,8 +1,10 @@
 """Linear layers: ``y = x @ W^T + b``.
 
-On CUDA with bf16 operands whose shapes fit the tile constraints the product runs on the hand-written
-tcgen05 / TMEM / TMA GEMM of ``csrc/gemm_tcgen05.cu`` (:mod:`tspipe_b200.ops.gemm`), forward and both
-backward products; everything else goes to the library GEMM.
+On CUDA under bf16 compute, layers whose shapes fit the tile constraints (feature counts multiples of 64, at least
+128 rows) run on the hand-written tcgen05 / TMEM / TMA kernels - forward on the CTA-pair GEMM with the bias in its
+epilogue, both backward products on the implicit-GEMM kernels (:mod:`tspipe_b200.ops.gemm`).  Everything else
+(CPU, fp32 compute, odd shapes) goes to the library GEMM.  Reference call sites: every ``nn.Linear`` of
+`benchmarks/moco-v3/vits.py`, `benchmarks/distilbert/bert.py:104-266`, `benchmarks/byol/models/mlp_head.py:4-26`.
 """
 from __future__ import annotations
 
@@ -11,11 +13,13 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-_USE_TCGEN05 = False
+import os
+
+_USE_TCGEN05 = os.environ.get("TSPIPE_LINEAR", "tcgen05") != "library"      # TSPIPE_LINEAR=library: A/B runs
 
 
 def set_tcgen05(flag: bool) -> None:
-    """Route eligible linears through the tcgen05 kernel (off by default)."""
+    """Route eligible linears through the tcgen05 kernels (default) or always through the library."""
     global _USE_TCGEN05
     _USE_TCGEN05 = bool(flag)
 

@@ -964,7 +964,9 @@ class StageEngine:
                 torch.clear_autocast_cache()
             if self.cuda:
                 from ..ops import conv as _conv
-                _conv.clear_weight_cache()          # bf16 weight copies of the tcgen05 convolutions
+                from ..ops import gemm as _gemm
+                _conv.clear_weight_cache()          # bf16 weight copies of the tcgen05 convolutions ...
+                _gemm.clear_weight_cache()          # ... and linear layers
             self.steps_done += 1
 
     def _dp_sync(self) -> None:

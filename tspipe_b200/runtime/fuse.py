@@ -7,7 +7,8 @@ children in order but lets neighbouring ones share a kernel:
 
 * ``BatchNorm -> ReLU``                      one fused normalise + activation pass (``ops.bn.bn_act``);
 * ``Conv2d(3, 64, 7, stride 2) -> BatchNorm`` the tcgen05 stem convolution, whose epilogue already produces the
-  BatchNorm statistics (``ops.conv.stem_conv``), so the statistics pass over the activation disappears.
+  BatchNorm statistics (``ops.conv.stem_conv``), so the statistics pass over the activation disappears;
+* ``Linear`` children (the MLP heads)        the tcgen05 GEMM path of ``ops.linear.linear``, forward and backward.
 
 The reference runs these layers one library call at a time
 (`benchmarks/byol/models/resnet_base_network.py`, `tspipe/tspipe.py:553-580` for the child granularity).
@@ -27,6 +28,7 @@ class FusedSequential(nn.Sequential):
     def forward(self, x: Any) -> Any:  # type: ignore[override]
         from ..ops import bn as _bn
         from ..ops import conv as _conv
+        from ..ops import linear as _linear
         mods: List[nn.Module] = list(self._modules.values())
         i, n = 0, len(mods)
         while i < n:
@@ -49,6 +51,10 @@ class FusedSequential(nn.Sequential):
                     and _bn.applicable(m, x):
                 x = _bn.bn_act(m, x, relu=True)
                 i += 2
+                continue
+            if type(m) is nn.Linear and isinstance(x, torch.Tensor):
+                x = _linear.linear(x, m.weight, m.bias)
+                i += 1
                 continue
             x = m(x)
             i += 1

@@ -412,6 +412,11 @@ class SplitKDEngine:
         if self.optimizer is not None:
             self.optimizer.step()
         self.flat.zero_grad()
+        if self.cuda:
+            from ..ops import conv as _conv
+            from ..ops import gemm as _gemm
+            _conv.clear_weight_cache()              # bf16 weight copies of the tcgen05 convolutions and linears
+            _gemm.clear_weight_cache()
 
     def _drain(self) -> None:
         for link in (self.fwd_out, self.bwd_out):
