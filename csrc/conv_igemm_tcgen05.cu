@@ -209,17 +209,6 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
               *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) << 4)) = q;
             }
             __syncwarp();
-            if (STATS) {
-              // column sums of the rounded block (rows that are not stored hold zeros): this lane owns columns
-              // 2 * lane and 2 * lane + 1
-#pragma unroll
-              for (int rr = 0; rr < 32; ++rr) {
-                const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
-                                                                       (lane & 3) * 4);
-                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
-                cs[i][0] += f.x; cs[i][1] = fmaf(f.x, f.x, cs[i][1]); cs[i][2] += f.y; cs[i][3] = fmaf(f.y, f.y, cs[i][3]);
-              }
-            }
             if (tma_out) {
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
@@ -235,6 +224,18 @@ __device__ __forceinline__ void fwd_epilogue(const Geom& g, int num_tiles, int t
                 if (off >= 0) *reinterpret_cast<uint4*>(out + ((int64_t)off << 3) + col + pc * 8) = q;
               }
               __syncwarp();
+            }
+            // (the block's stores are on their way: the sums overlap them)
+            if (STATS) {
+              // column sums of the rounded block (rows that are not stored hold zeros): this lane owns columns
+              // 2 * lane and 2 * lane + 1
+#pragma unroll 8
+              for (int rr = 0; rr < 32; ++rr) {
+                const uint32_t wv = *reinterpret_cast<const uint32_t*>(buf + rr * 128 + (((lane >> 2) ^ (rr & 7)) << 4) +
+                                                                       (lane & 3) * 4);
+                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wv));
+                cs[i][0] += f.x; cs[i][1] = fmaf(f.x, f.x, cs[i][1]); cs[i][2] += f.y; cs[i][3] = fmaf(f.y, f.y, cs[i][3]);
+              }
             }
           }
         }
