@@ -10,7 +10,10 @@ tqdm.  Nothing from ``tspipe_b200`` is imported on this path.
 
 Configuration: fp32 as shipped (the reference has no mixed-precision path in its pipeline), one
 pipeline over all N GPUs with its fixed N-1 microbatches; for N = 1 its GPipe-emulation mode with one
-microbatch, because its scheduler needs at least two stages (``tspipe/tspipe.py:106-111``).
+microbatch, because its scheduler needs at least two stages (``tspipe/tspipe.py:106-111``).  A second run
+(``reference_bf16`` in the output line) gives the reference the precision the own arm computes in: every child of
+the Sequentials handed to the stock ``tspipe.TSPipe`` is wrapped so that its forward runs under
+``torch.autocast(bfloat16)`` (``baseline/ref_wrappers.py``); nothing under ``baseline/_ref`` is edited.
 
 Timing: the reference reports each batch's loss to the feeding process after a device synchronisation
 (``tspipe/gpu_task.py:180,204``).  The harness records the host time at which ``feed`` hands back the
@@ -53,38 +56,52 @@ def run_reference(a) -> None:
                                                          "GROUP_WORLD_SIZE", "ROLE_WORLD_SIZE", "ROLE_NAME",
                                                          "OMP_NUM_THREADS"))}
     env["CUDA_VISIBLE_DEVICES"] = ",".join(str(i) for i in range(a.gpus))
-    cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(a.gpus), "--steps", str(a.steps),
-           "--warmup", str(a.warmup), "--per-gpu-batch", str(a.per_gpu_batch)]
-    limit = int(os.environ.get("TSPIPE_REF_TIMEOUT", 600))
-    import signal
-    proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
-                            start_new_session=True)
-    try:
-        out, err = proc.communicate(timeout=limit)
-    except subprocess.TimeoutExpired:
-        out, err = "", ""
-    finally:
-        try:                        # the reference leaves worker processes behind when it fails
-            os.killpg(proc.pid, signal.SIGKILL)
-        except ProcessLookupError:
-            pass
-    if proc.poll() is None:
-        proc.wait()
+    per_gpu = getattr(a, "per_gpu_batch", 0) or 128
+    want = getattr(a, "ref_dtype", "both")
 
-    class _R:
-        pass
-    res = _R()
-    res.stdout, res.stderr, res.returncode = out, err, proc.returncode
-    log = os.environ.get("TSPIPE_REF_LOG")
-    if log:
-        with open(log, "w") as f:
-            f.write(out + "\n---- stderr ----\n" + err)
-    if not out and not err:
-        return unavailable(f"the reference run did not finish within {limit} s on {a.gpus} GPU(s)")
-    line = next((l for l in reversed(res.stdout.splitlines()) if l.startswith('{"metric"')), None)
+    def one(dtype: str):
+        """Run the reference once in a fresh process group; returns (json line or None, failure text)."""
+        cmd = [sys.executable, os.path.abspath(__file__), "--gpus", str(a.gpus), "--steps", str(a.steps),
+               "--warmup", str(a.warmup), "--per-gpu-batch", str(per_gpu), "--ref-dtype", dtype]
+        limit = int(os.environ.get("TSPIPE_REF_TIMEOUT", 600))
+        import signal
+        proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                                start_new_session=True)
+        try:
+            out, err = proc.communicate(timeout=limit)
+        except subprocess.TimeoutExpired:
+            out, err = "", ""
+        finally:
+            try:                        # the reference leaves worker processes behind when it fails
+                os.killpg(proc.pid, signal.SIGKILL)
+            except ProcessLookupError:
+                pass
+        if proc.poll() is None:
+            proc.wait()
+        log = os.environ.get("TSPIPE_REF_LOG")
+        if log:
+            with open(log + ("" if dtype == "fp32" else "." + dtype), "w") as f:
+                f.write(out + "\n---- stderr ----\n" + err)
+        if not out and not err:
+            return None, f"the reference run did not finish within {limit} s on {a.gpus} GPU(s)"
+        line = next((l for l in reversed(out.splitlines()) if l.startswith('{"metric"')), None)
+        if line is None:
+            tail = (err or out).strip().splitlines()[-3:]
+            return None, f"the reference run failed (exit {proc.returncode}): {' | '.join(tail)}"
+        return line, ""
+
+    line, why = one("bf16" if want == "bf16" else "fp32")
     if line is None:
-        tail = (res.stderr or res.stdout).strip().splitlines()[-3:]
-        return unavailable(f"the reference run failed (exit {res.returncode}): {' | '.join(tail)}")
+        return unavailable(why)
+    if want == "both":
+        line16, why16 = one("bf16")
+        rec = json.loads(line)
+        if line16 is not None:
+            r16 = json.loads(line16)
+            rec["reference_bf16"] = {k: r16[k] for k in ("value", "unit", "ms_per_step", "dtype")}
+        else:
+            rec["reference_bf16"] = {"unavailable": why16[:300]}
+        line = json.dumps(rec)
     print(line, flush=True)
 
 
@@ -96,8 +113,10 @@ def child() -> None:
     p.add_argument("--steps", type=int, required=True)
     p.add_argument("--warmup", type=int, required=True)
     p.add_argument("--per-gpu-batch", type=int, default=128)
+    p.add_argument("--ref-dtype", default="fp32", choices=["fp32", "bf16"])
     a, _ = p.parse_known_args()
 
+    sys.path.insert(0, HERE)
     sys.path.insert(0, REF)
     sys.path.insert(0, os.path.join(REF, "tspipe_ref_byol"))
     import torch
@@ -140,6 +159,9 @@ def child() -> None:
     # layers whenever both end up in one partition (always the case on 1 GPU), so give them names of their own.
     from collections import OrderedDict
     predictor = torch.nn.Sequential(OrderedDict((f"pred{i}", m) for i, m in enumerate(predictor.children())))
+    if a.ref_dtype == "bf16":
+        from ref_wrappers import autocast_children
+        online, target, predictor = autocast_children(online), autocast_children(target), autocast_children(predictor)
     batch = a.per_gpu_batch * n
     opt = LARS(list(online.parameters()) + list(predictor.parameters()), lr=0.2 * batch / 256, momentum=0.9,
                weight_decay=1.5e-6)
@@ -173,12 +195,21 @@ def child() -> None:
         dt = stamp[W + K] - stamp[W]
         out = {"metric": "BYOL ResNet-50 training throughput", "value": round(batch * K / dt, 2), "unit": "images/s",
                "n_gpus": n, "steps": K, "warmup": W, "ms_per_step": round(dt / K * 1e3, 3), "higher_is_better": True,
-               "scaling": "weak", "vs_baseline": None, "dtype": "fp32 (as shipped; TF32 convolutions by PyTorch default)",
+               "scaling": "weak", "vs_baseline": None,
+               "dtype": "fp32 (as shipped; TF32 convolutions by PyTorch default)" if a.ref_dtype == "fp32"
+                        else "bf16 (every Sequential child's forward under torch.autocast; fp32 parameters)",
                "data": "synthetic", "impl": "reference",
                "config": {"model": "byol_resnet50+mlp4096-256", "global_batch": batch, "seq_len": None, "image": 224,
-                          "parallelism": f"pp{n}" + (" (gpipe_emulation, 1 microbatch)" if n == 1 else f" ({n - 1} microbatches)"),
-                          "optimizer": "LARS", "ema": 0.996,
-                          "timing": "host time between the arrivals of the losses of batch W and batch W+K"}}
+                          "parallelism": f"pp{n}" + (" (gpipe_emulation)" if n == 1 else ""),
+                          "microbatches": 1 if n == 1 else n - 1, "bwd_split": 1 if n == 1 else 2,
+                          "optimizer": "LARS", "ema": 0.996, "views": "one forward per view",
+                          "l2_policy": "inputs larger than L2 (a step's activations are several GB per GPU)",
+                          "timing": "host time between the arrivals of the losses of batch W and batch W+K"},
+               # the reference's number IS end to end: every step its feed() ships the two fp32 views from shared
+               # host memory to the first stage and the loss comes back to the feeding process as a Python float
+               "e2e": {"value": round(batch * K / dt, 2), "unit": "images/s", "ms_per_step": round(dt / K * 1e3, 3),
+                       "h2d_bytes_per_step": 2 * batch * 3 * 224 * 224 * 4, "d2h_bytes_per_step": 4,
+                       "api": "tspipe.TSPipe.feed(shared-memory host views) per step; loss float back per step"}}
         print(json.dumps(out), flush=True)
     try:
         tsp.stop()

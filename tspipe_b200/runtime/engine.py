@@ -998,7 +998,7 @@ def _bn_segments(n: int):
 
 
 def _to_conv_input(t: torch.Tensor) -> torch.Tensor:
-    if t.dim() == 4 and t.dtype == torch.float32:
+    if t.dim() == 4 and t.dtype in (torch.float32, torch.bfloat16):
         return t.to(dtype=torch.bfloat16, memory_format=torch.channels_last)
     return t
 
