@@ -8,8 +8,12 @@
 //   * it sums that range of every replica's gradient buffer with plain peer loads (the reduce-scatter),
 //   * updates parameter and optimizer state of the range,
 //   * and stores the new parameters into every replica's parameter buffer with peer stores (the all-gather).
-// Ordering against the peers' backward passes and next forward passes is established by the caller with
-// stream-ordered collectives; nothing in here spins on a flag.
+// Ordering between the ranks (peers' backward passes done -> gradient reads; reads done -> parameter stores; stores
+// done -> next forward) goes through signal words in peer-mapped memory: a rank announces a phase by storing an
+// increasing counter into slot [its index] of every peer's pad (tsp_signal_arrive), and waits for a phase by spinning,
+// with a time limit, until every slot of its own pad has reached the counter (tsp_signal_wait).  A wait that runs out
+// records a code in a status word and the kernel returns: nothing traps, nothing hangs.  Every rank runs on its own
+// GPU, so a waiting kernel never shares a GPU with the kernel it waits for.
 #include "common.cuh"
 #include "tspipe_kernels.h"
 
@@ -195,6 +199,64 @@ __global__ void __launch_bounds__(kThreads) dp_adamw_kernel(PeerPtrs grads, Peer
   }
 }
 
+// ---- signal words ------------------------------------------------------------------------------------------------
+struct PadPtrs {
+  int* p[kMaxPeers];
+};
+
+// everything this stream did before is visible to the peers before they can see the counter
+__global__ void signal_arrive_kernel(PadPtrs pads, int n_peers, int self, int value) {
+  const int r = threadIdx.x;
+  if (r < n_peers) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(pads.p[r] + self), "r"(value) : "memory");
+  }
+}
+
+__device__ __forceinline__ unsigned long long timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// thread r waits until slot r of this rank's pad has reached `value`; gives up after limit_ns
+__global__ void signal_wait_kernel(const int* __restrict__ pad, int n_peers, int value, unsigned long long limit_ns,
+                                   int* __restrict__ status, int code) {
+  const int r = threadIdx.x;
+  if (r >= n_peers) return;
+  const unsigned long long t0 = timer_ns();
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(seen) : "l"(pad + r) : "memory");
+    if (seen - value >= 0) break;                    // counters only grow (wrap-safe comparison)
+    if (timer_ns() - t0 > limit_ns) {
+      atomicCAS(status, 0, code);
+      break;
+    }
+    __nanosleep(200);
+  }
+  __threadfence_system();
+}
+
+// each rank's partial LARS norms go to slot [self] of every peer's table: dst_r[self * n + i] = norms[i]
+__global__ void __launch_bounds__(kThreads) publish_norms_kernel(PeerPtrs tables, int n_peers, int self,
+                                                                 const float* __restrict__ norms, int n) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n * n_peers; i += gridDim.x * blockDim.x) {
+    const int r = i / n, k = i - r * n;
+    tables.p[r][(int64_t)self * n + k] = norms[k];
+  }
+}
+
+// norms[i] = sum over ranks of table[r * n + i]
+__global__ void __launch_bounds__(kThreads) sum_norms_kernel(const float* __restrict__ table, int n_peers, int n,
+                                                             float* __restrict__ norms) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int r = 0; r < n_peers; ++r) s += table[(int64_t)r * n + i];
+    norms[i] = s;
+  }
+}
+
 // dst[r * n + i] = src_r[i]: concatenate one equally sized block per peer (16-byte units) into local memory.
 __global__ void __launch_bounds__(kThreads) gather_blocks_kernel(PeerPtrs srcs, int n_peers, int64_t n16,
                                                                  uint4* __restrict__ dst) {
@@ -263,6 +325,41 @@ int tsp_gather_blocks(void* const* srcs, int n_peers, int64_t bytes_each, void* 
   int64_t blocks = (n16 * n_peers + kThreads - 1) / kThreads;
   if (blocks > 148 * 8) blocks = 148 * 8;
   gather_blocks_kernel<<<(int)blocks, kThreads, 0, stream>>>(sp, n_peers, n16, (uint4*)dst);
+  return TSP_LAUNCH_CHECK();
+}
+
+// Store `value` into slot [self] of every rank's signal pad (pads[r] = rank r's pad of >= n_peers ints, own pad
+// included).  Stream-ordered: everything enqueued before on `stream` is visible to a peer that sees the value.
+int tsp_signal_arrive(void* const* pads, int n_peers, int self, int value, cudaStream_t stream) {
+  if (n_peers < 1 || n_peers > kMaxPeers || self < 0 || self >= n_peers) return -3;
+  PadPtrs pp;
+  for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = i < n_peers ? (int*)pads[i] : nullptr;
+  signal_arrive_kernel<<<1, 32, 0, stream>>>(pp, n_peers, self, value);
+  return TSP_LAUNCH_CHECK();
+}
+
+// Wait on `stream` until every one of the n_peers slots of this rank's pad has reached `value`, at most limit_ms
+// milliseconds.  When the limit runs out, *status (one zeroed int in device memory) becomes `code` and the kernel
+// returns normally; the caller reads the status word.
+int tsp_signal_wait(const void* pad, int n_peers, int value, int limit_ms, int* status, int code, cudaStream_t stream) {
+  if (n_peers < 1 || n_peers > kMaxPeers || limit_ms < 1) return -3;
+  signal_wait_kernel<<<1, 32, 0, stream>>>((const int*)pad, n_peers, value, (unsigned long long)limit_ms * 1000000ull,
+                                           status, code);
+  return TSP_LAUNCH_CHECK();
+}
+
+// All-gather of the per-rank partial LARS norms through peer stores: tables[r] = rank r's [n_peers][n] table.
+int tsp_publish_norms(void* const* tables, int n_peers, int self, const float* norms, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  PeerPtrs tp;
+  if (!fill(tp, tables, n_peers) || self < 0 || self >= n_peers) return -3;
+  publish_norms_kernel<<<(n * n_peers + kThreads - 1) / kThreads, kThreads, 0, stream>>>(tp, n_peers, self, norms, n);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_sum_norms(const float* table, int n_peers, int n, float* norms, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  sum_norms_kernel<<<(n + kThreads - 1) / kThreads, kThreads, 0, stream>>>(table, n_peers, n, norms);
   return TSP_LAUNCH_CHECK();
 }
 

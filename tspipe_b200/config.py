@@ -26,6 +26,10 @@ New optional keys (all defaulted so reference YAML files load unchanged):
 ``runtime.merge_views``      single stage, one microbatch: run both views of a network as one stacked forward /
                              backward with per-view BatchNorm statistics (default True)
 ``runtime.cuda_graphs``      replay the teacher's stage forward from a CUDA graph (default False)
+``runtime.dp_signals``       order the fused data-parallel kernels with device-side signal words in peer memory
+                             (bounded waits) instead of tiny NCCL collectives (default True)
+``runtime.dp_early_reduce``  start the data-parallel gradient reduction on a side stream right after the backward
+                             wave, behind the look-ahead teacher forward (default True)
 ``runtime.heartbeat_s`` / ``runtime.timeout_s``  failure-detection heartbeat period / deadline
 """
 from __future__ import annotations
@@ -43,7 +47,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True},
 }
 
 

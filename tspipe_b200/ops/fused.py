@@ -362,6 +362,28 @@ def dp_reduce_norms_(grad_ptrs, n_peers, scale, g_out, p, chunks, seg_hp, norms)
 
 
 @torch.no_grad()
+def publish_norms_(table_ptrs, n_peers, self_idx, norms) -> None:
+    """This rank's partial LARS norms into slot ``self_idx`` of every replica's table (peer stores)."""
+    L = lib()
+    L.tsp_publish_norms.restype = _c.c_int
+    with torch.cuda.device(norms.device):
+        _check(L.tsp_publish_norms(table_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _ptr(norms),
+                                   _c.c_int(norms.numel()), _stream()), "tsp_publish_norms")
+    _count()
+
+
+@torch.no_grad()
+def sum_norms_(table, n_peers, norms) -> None:
+    """``norms = sum_r table[r]`` over the replicas' slots."""
+    L = lib()
+    L.tsp_sum_norms.restype = _c.c_int
+    with torch.cuda.device(norms.device):
+        _check(L.tsp_sum_norms(_ptr(table), _c.c_int(n_peers), _c.c_int(norms.numel()), _ptr(norms), _stream()),
+               "tsp_sum_norms")
+    _count()
+
+
+@torch.no_grad()
 def dp_lars_apply_(param_ptrs, n_peers, self_idx, g, mu, chunks, seg_hp, norms) -> None:
     L = lib()
     L.tsp_dp_lars_apply.restype = _c.c_int

@@ -60,12 +60,38 @@ class _FlatMixin:
                         params=pointer_table(peer_params), keep=(list(peer_grads), list(peer_params)),
                         chunks=fused.build_chunks(self.flat.offsets, self.flat.numels, self.flat.device,
                                                   self_index * shard, (self_index + 1) * shard),
-                        token=torch.zeros(1, device=self.flat.device))
+                        token=torch.zeros(1, device=self.flat.device), phase=0, reduced=False, signals=None)
         self.handles_dp = True
 
+    def enable_signals(self, pad, norm_tables=None) -> None:
+        """Order the data-parallel kernels with device-side signals (:class:`tspipe_b200.comm.signals.SignalPad`)
+        instead of tiny NCCL collectives; ``norm_tables`` = every replica's ``[R][2 * n_tensors]`` table through
+        which LARS exchanges its partial norms with peer stores."""
+        from ..comm.peer import pointer_table
+        d = self._dp
+        d["signals"] = pad
+        if norm_tables is not None:
+            d["norm_tables"] = pointer_table(norm_tables)
+            d["norm_keep"] = list(norm_tables)
+            d["norm_table"] = norm_tables[d["idx"]]
+
     def _dp_barrier(self) -> None:
+        """All replicas have reached this point of their streams (and what they enqueued before it is visible)."""
+        d = self._dp
+        if d["signals"] is not None:
+            d["phase"] += 1
+            d["signals"].arrive(d["phase"])
+            d["signals"].wait(d["phase"])
+            return
         import torch.distributed as dist
-        dist.all_reduce(self._dp["token"], group=self._dp["group"])
+        dist.all_reduce(d["token"], group=d["group"])
+
+    def dp_reduce(self, grad_scale: float = 1.0) -> None:
+        """First half of the data-parallel step, callable as soon as this replica's backward is complete (and on
+        another stream than the one that goes on computing): wait for every replica's backward, sum this rank's
+        range of all gradient buffers, and for LARS exchange the partial norms.  :meth:`step` skips this half when
+        it has already run for the step."""
+        raise NotImplementedError
 
     def _buf(self, name: str) -> torch.Tensor:
         if name not in self._flat_state:
@@ -148,13 +174,14 @@ class LARS(_FlatMixin, Optimizer):
             rows = [[g["lr"], g["weight_decay"], g["momentum"], g["trust_coefficient"], 1.0 if p.ndim > 1 else 0.0]
                     for p, g in zip(flat.params, self._seg_group)]
             if self.handles_dp:
-                import torch.distributed as dist
                 d = self._dp
                 hp = self._hp_table(rows)
-                self._dp_barrier()                      # every replica's backward is complete
-                fused.dp_reduce_norms_(d["grads"], d["r"], grad_scale / d["r"], flat.grad, flat.data, d["chunks"], hp,
-                                       self._norms)
-                dist.all_reduce(self._norms, group=d["group"])     # whole-tensor norms; also: all gradient reads done
+                if not d["reduced"]:
+                    self.dp_reduce(grad_scale)
+                d["reduced"] = False
+                if d["signals"] is not None and "norm_table" in d:
+                    d["signals"].wait(d["phase"])       # every replica's norms are here and all gradient reads done
+                    fused.sum_norms_(d["norm_table"], d["r"], self._norms)
                 fused.dp_lars_apply_(d["params"], d["r"], d["idx"], flat.grad, mu, d["chunks"], hp, self._norms)
                 self._dp_barrier()                      # every replica's parameters are complete
                 return
@@ -166,6 +193,26 @@ class LARS(_FlatMixin, Optimizer):
         if self.teacher_flat is not None:
             n = self.teacher_flat.numel()
             self.teacher_flat.lerp_(flat.data[:n], 1.0 - self.ema_momentum)
+
+    @torch.no_grad()
+    def dp_reduce(self, grad_scale: float = 1.0) -> None:
+        import torch.distributed as dist
+        from ..ops import fused
+        flat, d = self.flat, self._dp
+        rows = [[g["lr"], g["weight_decay"], g["momentum"], g["trust_coefficient"], 1.0 if p.ndim > 1 else 0.0]
+                for p, g in zip(flat.params, self._seg_group)]
+        hp = self._hp_table(rows)
+        self._dp_barrier()                              # every replica's backward is complete
+        fused.dp_reduce_norms_(d["grads"], d["r"], grad_scale / d["r"], flat.grad, flat.data, d["chunks"], hp,
+                               self._norms)
+        if d["signals"] is not None and "norm_table" in d:
+            # partial norms to every replica's table, then the signal that they (and this rank's reads) are done
+            fused.publish_norms_(d["norm_tables"], d["r"], d["idx"], self._norms)
+            d["phase"] += 1
+            d["signals"].arrive(d["phase"])
+        else:
+            dist.all_reduce(self._norms, group=d["group"])     # whole-tensor norms; also: all gradient reads done
+        d["reduced"] = True
 
     @staticmethod
     def _lars_one(p, dp, mu, g):
@@ -207,7 +254,11 @@ class AdamW(_FlatMixin, Optimizer):
                      1.0 - g["betas"][0] ** t, 1.0 - g["betas"][1] ** t] for g in self._seg_group]
             if self.handles_dp:
                 d = self._dp
-                self._dp_barrier()
+                if not d["reduced"]:
+                    self.dp_reduce(grad_scale)
+                d["reduced"] = False
+                if d["signals"] is not None:
+                    d["signals"].wait(d["phase"])       # every replica's backward is complete
                 fused.dp_adamw_step_(d["grads"], d["params"], d["r"], d["idx"], grad_scale / d["r"], m, v, d["chunks"],
                                      self._hp_table(rows))
                 self._dp_barrier()
@@ -220,6 +271,18 @@ class AdamW(_FlatMixin, Optimizer):
         if self.teacher_flat is not None:
             n = self.teacher_flat.numel()
             self.teacher_flat.lerp_(flat.data[:n], 1.0 - self.ema_momentum)
+
+    @torch.no_grad()
+    def dp_reduce(self, grad_scale: float = 1.0) -> None:
+        """AdamW reduces, updates and stores in one kernel, so its early half only announces that this replica's
+        gradients are complete (with signals) or waits for all of them (collectives)."""
+        d = self._dp
+        if d["signals"] is not None:
+            d["phase"] += 1
+            d["signals"].arrive(d["phase"])
+        else:
+            self._dp_barrier()
+        d["reduced"] = True
 
     @staticmethod
     def _adamw_one(p, grad, m, v, g, t):

@@ -257,6 +257,8 @@ class StageEngine:
         self.flat_target = FlatParams([p for p in self.target.parameters()], self.device, with_grad=False)
         self._bind_optimizer()
         self.dp_fused = False
+        self.dp_signals = None
+        self._dp_event = None
         self._enable_dp_fused()
         self.ema_plan = ema_plan
         self.updater = self._make_updater(target_update_fn)
@@ -327,6 +329,18 @@ class StageEngine:
         grads = peer.exchange(self.flat_online.grad, topo.dp_group, topo.dp_ranks)
         params = peer.exchange(self.flat_online.data, topo.dp_group, topo.dp_ranks)
         opt.enable_dp(topo.dp_group, grads, params, topo.replica)
+        if self.cfg["runtime"].get("dp_signals", True):
+            # ordering between the replicas through signal words in peer memory (bounded device-side waits) instead
+            # of tiny NCCL collectives; LARS exchanges its partial norms through peer stores as well
+            from ..comm.signals import SignalPad
+            limit_ms = int(min(max(float(self.cfg["runtime"]["timeout_s"]), 1.0), 120.0) * 1000)
+            self.dp_signals = SignalPad(topo.dp_group, topo.dp_ranks, topo.replica, self.device, limit_ms=limit_ms)
+            tables = None
+            if type(opt).__name__ == "LARS":
+                table = torch.zeros(topo.dp * 2 * max(len(self.flat_online.params), 1), dtype=torch.float32,
+                                    device=self.device)
+                tables = peer.exchange(table, topo.dp_group, topo.dp_ranks)
+            opt.enable_signals(self.dp_signals, tables)
         self.dp_fused = True
 
     def _make_updater(self, fn: Optional[Callable]) -> TeacherUpdater:
@@ -502,8 +516,12 @@ class StageEngine:
                 if self.on_flushed is not None:
                     self.on_flushed(b - 1)
                 continue
+            prev_kind = None
             for op in self._block_ops(b):
+                if prev_kind == OpKind.B and op.kind != OpKind.B:
+                    self._dp_reduce_early()         # this replica's gradients of batch b are complete
                 self._dispatch(op)
+                prev_kind = op.kind
             self._retire(b)
             b += 1
 
@@ -584,24 +602,27 @@ class StageEngine:
         return data
 
     def _can_merge_views(self, rt: Dict[str, Any]) -> bool:
-        """Single stage, two views, one microbatch: both views of a network go through it as ONE forward (and one
-        backward) over the stacked batch.  Every BatchNorm keeps per-view statistics (``ops.bn.segments``), so the
-        numbers are those of two separate forwards; the kernels are twice as large and half as many, which is
-        what a B200 needs at 128 samples per view.  Requires that all batch-statistics layers are
-        :class:`DeferredBatchNorm` (the only ones that know about stacked views)."""
+        """Two views, no nano-batch split: both views of a microbatch go through every stage as ONE forward (and
+        one backward) over the stacked batch, and cross every stage boundary as one stacked item: the schedule's
+        items of view 0 carry both views, its items of view 1 are skipped on every stage.  Every BatchNorm keeps
+        per-view statistics (``ops.bn.segments``), so the numbers are those of two separate forwards; the kernels
+        are twice as large and half as many, which is what a B200 needs at ~128 samples per view.  Requires that
+        all batch-statistics layers are :class:`DeferredBatchNorm` (the only ones that know about stacked views);
+        all ranks must agree, so the decision is the minimum over the job."""
         from ..batchnorm import DeferredBatchNorm
         from torch.nn.modules.batchnorm import _BatchNorm
-        if not (rt.get("merge_views", True) and not self.kd and self.topo.pp == 1 and self.U == 1 and self.S == 1):
-            return False
-        if len(self.spec.student_views) != 2 or len(self.spec.teacher_views) != 2:
-            return False
-        for net in (self.online, self.target):
-            for m in net.modules():
-                if isinstance(m, _BatchNorm) and not isinstance(m, DeferredBatchNorm):
-                    return False
-                if isinstance(m, (nn.InstanceNorm1d, nn.InstanceNorm2d, nn.InstanceNorm3d)):
-                    continue
-        return True
+        ok = bool(rt.get("merge_views", True) and not self.kd and self.S == 1
+                  and len(self.spec.student_views) == 2 and len(self.spec.teacher_views) == 2)
+        if ok:
+            for net in (self.online, self.target):
+                for m in net.modules():
+                    if isinstance(m, _BatchNorm) and not isinstance(m, DeferredBatchNorm):
+                        ok = False
+        if self.topo.world > 1 and (self.topo.pp > 1):
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(int(flag.item()))
+        return ok
 
     def _conv_input(self) -> bool:
         """True when both networks start with a convolution under bf16 autocast: the cast that autocast would
@@ -649,8 +670,8 @@ class StageEngine:
         b = start
         while True:
             for o in batch_block(self.spec, self.topo.stage, b, None, fill=self._is_fill(b)):
-                if o.kind in (OpKind.T, OpKind.O):
-                    yield o
+                if o.kind in (OpKind.T, OpKind.O) and not (self.merge_views and o.view != 0):
+                    yield o                 # (stacked views: the item of view 0 carries both, view 1 never crosses)
             b += 1
 
     def _next_fwd_key(self, blocking: bool) -> Optional[Op]:
@@ -739,7 +760,7 @@ class StageEngine:
                     stored_out.append(oleaves)
             if not teacher:
                 self.acts[(op.batch, op.view, op.ub)] = _Stored(stored_in, stored_out, gin_idx, gout_idx)
-            if merged:
+            if merged and last:
                 # the loss sees the two views as two outputs again (halves of the stacked batch)
                 for v in (0, 1):
                     half = pt.tree_map_tensors(lambda t, v=v: t.chunk(2)[v] if t.dim() > 0 else t, outs[0])
@@ -879,7 +900,7 @@ class StageEngine:
         st = self.acts[(b, v, ub)]
         with self._on_compute(), self._prof("backward", op):
             outs = [st.outputs[piece][i] for i in st.grad_out_idx]
-            if self.merge_views:
+            if self.merge_views and self.topo.is_last:
                 g0, g1 = self.out_grads.pop((b, 0, k)), self.out_grads.pop((b, 1, k))
                 grads = [torch.cat([a, c]) for a, c in zip(g0, g1)]
             elif self.topo.is_last:
@@ -904,7 +925,8 @@ class StageEngine:
         of the batch are posted too (their shapes are those of the stored stage outputs)."""
         order = self._bwd_order.get(op.batch)
         if order is None:
-            order = self.spec.backward_items(op.batch, self.topo.stage)
+            order = [o for o in self.spec.backward_items(op.batch, self.topo.stage)
+                     if not (self.merge_views and o.view != 0)]
             self._bwd_order = {op.batch: order}
         i = next(n for n, o in enumerate(order) if o.view == op.view and o.ub == op.ub)
         depth = int(self.cfg["runtime"].get("prefetch", 2))
@@ -944,6 +966,9 @@ class StageEngine:
                 self.flat_online.grad.div_(self.ga_count + 1)
                 self.ga_count = 0
             self._dp_sync()
+            if self._dp_event is not None:          # the early half of the data-parallel step ran on the side stream
+                torch.cuda.current_stream().wait_event(self._dp_event)
+                self._dp_event = None
             if hasattr(self.updater, "before_step"):
                 self.updater.before_step(self.momentum)
             if self.optimizer is not None:
@@ -968,6 +993,27 @@ class StageEngine:
                 _conv.clear_weight_cache()          # bf16 weight copies of the tcgen05 convolutions ...
                 _gemm.clear_weight_cache()          # ... and linear layers
             self.steps_done += 1
+
+    def _dp_reduce_early(self) -> None:
+        """Start the data-parallel gradient reduction as soon as the last backward item of the batch has been
+        enqueued, on the side stream: the schedule places the look-ahead teacher forwards of the next batch between
+        the backward wave and the optimizer step, so the peer reads (and the wait for the slowest replica) run
+        behind that forward instead of in front of the step.  DDP in the reference's baselines overlaps its
+        all-reduce buckets with backward (`benchmarks/moco-v3/main.py:249-254`); the pipelined runtime has none."""
+        opt = self.optimizer
+        if not (self.dp_fused and self.cuda and self.ga == 1 and not self.skip_optimizer
+                and hasattr(opt, "dp_reduce") and self._dp_event is None
+                and self.cfg["runtime"].get("dp_early_reduce", True)):
+            return
+        with self._on_compute():
+            self.flat_online.collect_stray_grads()
+            ready = torch.cuda.Event()
+            ready.record()
+        with torch.cuda.stream(self.dp_stream):
+            self.dp_stream.wait_event(ready)
+            opt.dp_reduce()
+            self._dp_event = torch.cuda.Event()
+            self._dp_event.record()
 
     def _dp_sync(self) -> None:
         if self.topo.dp_group is None:
