@@ -85,6 +85,8 @@ def parse(argv=None):
     p.add_argument("--placement", default="", choices=["", "colocated", "split"])
     p.add_argument("--trace", action="store_true", help="print per-operation device time totals of the timed pass")
     p.add_argument("--no-peer", action="store_true", help="NCCL all-reduce instead of the peer-memory DP kernels")
+    p.add_argument("--sm-reserve", type=int, default=-1, help="SMs left free of the persistent kernels (-1 = default)")
+    p.add_argument("--no-merge-views", action="store_true", help="one forward per view instead of stacked views")
     p.add_argument("--no-dp-signals", action="store_true", help="order the DP kernels with NCCL collectives")
     p.add_argument("--no-dp-early", action="store_true", help="reduce the gradients at the optimizer step only")
     p.add_argument("--conv", choices=["igemm", "library"], default=None,
@@ -279,7 +281,8 @@ def measure(a, pp, dp, ub, split, e2e, placement="colocated"):
            "runtime": {"num_ubatch": ub, "bwd_split": split, "dp_replicas": dp, "dtype": a.dtype,
                        "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300,
                        "peer_memory": not a.no_peer, "cuda_graphs": a.cuda_graphs, "placement": placement,
-                       "dp_signals": not a.no_dp_signals, "dp_early_reduce": not a.no_dp_early},
+                       "dp_signals": not a.no_dp_signals, "dp_early_reduce": not a.no_dp_early,
+                       "merge_views": not a.no_merge_views, "sm_reserve": None if a.sm_reserve < 0 else a.sm_reserve},
            "train": {"deferred_batch_norm": wl["deferred_bn"]}}
     from tspipe_b200.profiler import TSPipeProfiler
     prof = TSPipeProfiler(filename=f"/tmp/bench_trace_{rank}.csv").__enter__()

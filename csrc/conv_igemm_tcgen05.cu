@@ -763,6 +763,10 @@ __global__ void bounded_wait_probe_kernel(unsigned long long limit_ns, int code,
 // ---------------------------------------------------------------------------------------------------------------
 unsigned long long g_wait_ns = 2000000000ull;     // give-up time of the kernels' mbarrier waits (2 s)
 
+}  // namespace
+extern int g_tsp_sm_reserve;          // defined in peer.cu
+namespace {
+
 int sm_count() {
   static int n_sm[64] = {};
   int dev = 0;
@@ -772,7 +776,8 @@ int sm_count() {
     cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev);
     if (n_sm[dev] <= 0) n_sm[dev] = 148;
   }
-  return n_sm[dev];
+  const int n = n_sm[dev] - g_tsp_sm_reserve;       // SMs left to communication kernels stay free
+  return n > 8 ? n : 8;
 }
 
 // Pixel box for a w x h x n grid: at most max_pix pixels, as few tiles as possible, tiles of equal size where it

@@ -24,6 +24,8 @@
 #include "common.cuh"
 #include "tspipe_kernels.h"
 
+extern int g_tsp_sm_reserve;          // defined in peer.cu
+
 namespace {
 
 constexpr int kCout = 64;
@@ -455,7 +457,8 @@ int tsp_conv_stem_fwd(const void* x, const void* wmat, void* y, float* sums, int
     attr_set[dev] = true;
   }
   const int tiles = n * oh;
-  const int grid = tiles < n_sm[dev] ? tiles : n_sm[dev];
+  const int usable = n_sm[dev] - g_tsp_sm_reserve > 8 ? n_sm[dev] - g_tsp_sm_reserve : 8;
+  const int grid = tiles < usable ? tiles : usable;
   conv_stem_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tw, ty, (const __nv_bfloat16*)x, n, h, w, oh, ow, n / segs, sums, status);
   return TSP_LAUNCH_CHECK();
 }

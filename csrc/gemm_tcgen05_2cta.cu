@@ -23,6 +23,8 @@
 #include "tcgen05.cuh"
 #include "tspipe_kernels.h"
 
+extern int g_tsp_sm_reserve;          // defined in peer.cu
+
 namespace {
 
 constexpr int BM = 128;          // rows per CTA (pair tile: 256)
@@ -453,7 +455,8 @@ int launch(const void* a, const void* b, void* c, const float* bias, int m, int 
     attr_set[dev] = true;
   }
   const int num_tiles = ((n + BN - 1) / BN) * ((m + 2 * BM - 1) / (2 * BM));
-  int pairs = n_sm[dev] / 2;
+  int pairs = (n_sm[dev] - g_tsp_sm_reserve) / 2;      // SMs left to communication kernels stay free
+  if (pairs < 4) pairs = 4;
   if (pairs > num_tiles) pairs = num_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);

@@ -276,7 +276,18 @@ inline bool fill(PeerPtrs& dst, void* const* src, int n) {
 
 }  // namespace
 
+// SMs that the persistent tensor-core kernels leave free (see tsp_set_sm_reserve)
+int g_tsp_sm_reserve = 0;
+
 extern "C" {
+
+// The persistent tcgen05 kernels (convolutions, GEMMs) launch one CTA per SM with almost all of its shared memory; a
+// communication kernel that becomes ready while one of them runs (an NCCL send / receive of a stage link, a peer
+// reduction on a side stream) finds no SM until a CTA retires, i.e. until the whole persistent kernel ends.  With a
+// reserve of n, those kernels launch on (SM count - n) SMs and the rest stay available.  Set by the runtime when a
+// job has stage links; 0 for single-stage jobs.
+void tsp_set_sm_reserve(int n) { g_tsp_sm_reserve = n < 0 ? 0 : (n > 64 ? 64 : n); }
+int tsp_get_sm_reserve(void) { return g_tsp_sm_reserve; }
 
 // Make `peer_device`'s memory addressable from kernels of the current device.  0 = ok / already enabled,
 // -5 = the two devices have no peer path.

@@ -30,6 +30,8 @@ New optional keys (all defaulted so reference YAML files load unchanged):
                              (bounded waits) instead of tiny NCCL collectives (default True)
 ``runtime.dp_early_reduce``  start the data-parallel gradient reduction on a side stream right after the backward
                              wave, behind the look-ahead teacher forward (default True)
+``runtime.sm_reserve``       SMs the persistent tensor-core kernels leave free for communication kernels
+                             (default: 8 with stage links, 0 for single-stage jobs)
 ``runtime.heartbeat_s`` / ``runtime.timeout_s``  failure-detection heartbeat period / deadline
 """
 from __future__ import annotations
@@ -47,7 +49,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True, "sm_reserve": None},
 }
 
 

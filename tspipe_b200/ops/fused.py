@@ -34,6 +34,13 @@ def lib():
     return _lib
 
 
+def set_sm_reserve(n: int) -> None:
+    """Leave ``n`` SMs free of the persistent tcgen05 kernels (convolutions, GEMMs) so that communication kernels
+    that become ready while one of them runs - NCCL sends / receives of the stage links, peer reductions on a side
+    stream - find an SM at once instead of when the persistent kernel ends."""
+    lib().tsp_set_sm_reserve(_c.c_int(int(n)))
+
+
 def _count(n: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += n

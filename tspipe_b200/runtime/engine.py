@@ -233,6 +233,12 @@ class StageEngine:
         if self.cuda:
             from ..ops import bn as _bn
             _bn.set_enabled(self.fused)
+            if self.fused:
+                from ..ops import fused as _fused
+                reserve = rt.get("sm_reserve")
+                if reserve is None:             # stage links: their NCCL kernels must not wait for a persistent kernel
+                    reserve = 8 if topo.pp > 1 else 0
+                _fused.set_sm_reserve(int(reserve))
 
         self.online.to(self.device)
         self.target.to(self.device)
