@@ -326,6 +326,14 @@ int tsp_ipc_import(const unsigned char* handle64, void** base) {
 
 int tsp_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }
 
+// Stream-ordered copy between any two device addresses this process can reach (own memory or a mapped peer
+// buffer).  The driver moves the bytes with a copy engine over NVLink: no SM is involved, so a transfer never
+// competes with the persistent compute kernels for a place on the GPU.
+int tsp_copy_async(void* dst, const void* src, int64_t bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, stream);
+}
+
 // All-gather by peer loads: block r of `dst` receives `bytes_each` bytes read from srcs[r] (own or peer memory).
 int tsp_gather_blocks(void* const* srcs, int n_peers, int64_t bytes_each, void* dst, cudaStream_t stream) {
   if (bytes_each <= 0) return 0;

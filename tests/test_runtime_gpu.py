@@ -157,3 +157,58 @@ def test_teacher_cuda_graph_with_dict_stage_inputs_matches_eager():
     graphed = _kd_dict_job(True)
     assert len(eager) == len(graphed) == 6
     torch.testing.assert_close(torch.tensor(graphed), torch.tensor(eager), rtol=2e-2, atol=2e-2)
+
+
+def _byol_resnet_job(cuda_graphs: bool, ubatch: int, steps: int = 7):
+    """BYOL on a ResNet-18 trunk at 64x64, bf16 + channels-last (the own convolution / BatchNorm kernels), one GPU."""
+    import torch.distributed as dist
+    from tspipe_b200 import TSPipe
+    from tspipe_b200.losses import byol_loss, ema_update
+    from tspipe_b200.models.resnet import byol_networks
+    from tspipe_b200.optim import LARS
+    from tspipe_b200.ops import fused
+    os.environ.update(RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29535")
+    torch.manual_seed(0)
+    online, target, pred = byol_networks("resnet18", 256, 64)
+    opt = LARS(list(online.parameters()) + list(pred.parameters()), lr=0.05, weight_decay=1e-6, momentum=0.9)
+    cfg = {"runtime": {"num_ubatch": ubatch, "bwd_split": 1, "dtype": "bf16", "channels_last": True, "timeout_s": 120,
+                       "cuda_graphs": cuda_graphs},
+           "model_split": {"online": [len(online) + len(pred)], "target": [len(target)]},
+           "train": {"deferred_batch_norm": True}}
+    tsp = TSPipe(online, target, pred, opt, byol_loss, ema_update, 0.99, "", config=cfg, device="cuda:0")
+    g = torch.Generator().manual_seed(3)
+    losses, launches = [], []
+    for _ in range(steps):
+        a, b = torch.randn(32, 3, 64, 64, generator=g), torch.randn(32, 3, 64, 64, generator=g)
+        n0 = fused.LAUNCHES
+        l = tsp.feed(a.pin_memory(), b.pin_memory())
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    on, _ = tsp.state_dicts()
+    slots = tsp.engine.student_graphs.slots if tsp.engine.student_graphs is not None else {}
+    captured = sum(1 for s in slots.values() if s.fwd is not None)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return losses, on, captured
+
+
+@pytest.mark.parametrize("ubatch", [1, 2])
+def test_student_stage_cuda_graphs_match_eager(ubatch):
+    """``runtime.cuda_graphs``: after two eager calls per microbatch slot the student stage's forward and backward are
+    replayed from CUDA graphs (weights cast inside the graph, gradients added to the flat buffer inside the graph);
+    the losses and the trained weights are those of the eager run up to the noise of the atomically summed weight
+    gradients."""
+    eager, w_eager, n0 = _byol_resnet_job(False, ubatch)
+    again, w_again, _ = _byol_resnet_job(False, ubatch)          # the run-to-run noise of the eager path itself
+    graphed, w_graph, n1 = _byol_resnet_job(True, ubatch)
+    assert n0 == 0 and n1 == ubatch
+    assert len(eager) == len(graphed) == 7
+    torch.testing.assert_close(torch.tensor(graphed), torch.tensor(eager), rtol=2e-2, atol=2e-2)
+
+    def distance(x, y):
+        num = sum(float((x[0][k].float() - y[0][k].float()).pow(2).sum()) for k in y[0] if y[0][k].is_floating_point())
+        den = sum(float(y[0][k].float().pow(2).sum()) for k in y[0] if y[0][k].is_floating_point())
+        return (num / den) ** 0.5
+    noise = distance(w_again, w_eager)
+    assert distance(w_graph, w_eager) <= 3.0 * noise + 2e-3, (distance(w_graph, w_eager), noise)

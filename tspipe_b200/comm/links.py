@@ -43,19 +43,41 @@ class RecvHandle:
         return self.tensors
 
 
+def wire_form(t: torch.Tensor, channels_last: bool) -> torch.Tensor:
+    """The contiguous tensor whose bytes cross a link for ``t``.  With ``channels_last`` a 4-D tensor travels in NHWC
+    order (as an ``[N, H, W, C]`` view when it is already laid out that way - no copy), so that an activation of a
+    channels-last network is not transposed on the way out and back again on the way in."""
+    if channels_last and t.dim() == 4:
+        return t.permute(0, 2, 3, 1).contiguous()          # a view when t is channels-last
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def wire_empty(shape: Sequence[int], dtype: torch.dtype, device, channels_last: bool
+               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(buffer, tensor)``: the contiguous receive buffer of a tensor of ``shape`` and the tensor the consumer sees
+    (the same memory; NCHW-shaped with channels-last strides when ``channels_last`` applies)."""
+    if channels_last and len(shape) == 4:
+        n, c, h, w = shape
+        buf = torch.empty((n, h, w, c), dtype=dtype, device=device)
+        return buf, buf.permute(0, 3, 1, 2)
+    buf = torch.empty(tuple(shape), dtype=dtype, device=device)
+    return buf, buf
+
+
 class Link:
     """One direction of one stage boundary, as seen from one of its two ranks."""
 
-    def __init__(self, group, peer: int, device: torch.device):
+    def __init__(self, group, peer: int, device: torch.device, channels_last: bool = False):
         self.group, self.peer, self.device = group, peer, device
         self.cuda = device.type == "cuda"
+        self.channels_last = bool(channels_last)
         self.post_stream = torch.cuda.Stream(device) if self.cuda else None
         self._pending: Deque[Tuple[List[Any], List[torch.Tensor]]] = deque()
 
     # -- send ---------------------------------------------------------------------------------
     def send(self, tensors: Sequence[torch.Tensor]) -> None:
         """Enqueue sends ordered after the work already queued on the current stream."""
-        tensors = [t if t.is_contiguous() else t.contiguous() for t in tensors]
+        tensors = [wire_form(t, self.channels_last) for t in tensors]
         works = [dist.isend(t, self.peer, group=self.group) for t in tensors]
         self._pending.append((works, tensors))
         self._reap()
@@ -74,12 +96,12 @@ class Link:
     def post_recv(self, specs: Sequence[TensorSpec]) -> RecvHandle:
         if self.cuda:
             with torch.cuda.stream(self.post_stream):
-                bufs = [torch.empty(shape, dtype=dtype, device=self.device) for shape, dtype in specs]
-                works = [dist.irecv(b, self.peer, group=self.group) for b in bufs]
-            return RecvHandle(bufs, works, self.post_stream)
-        bufs = [torch.empty(shape, dtype=dtype) for shape, dtype in specs]
-        works = [dist.irecv(b, self.peer, group=self.group) for b in bufs]
-        return RecvHandle(bufs, works, None)
+                pairs = [wire_empty(shape, dtype, self.device, self.channels_last) for shape, dtype in specs]
+                works = [dist.irecv(b, self.peer, group=self.group) for b, _ in pairs]
+            return RecvHandle([t for _, t in pairs], works, self.post_stream)
+        pairs = [wire_empty(shape, dtype, None, self.channels_last) for shape, dtype in specs]
+        works = [dist.irecv(b, self.peer, group=self.group) for b, _ in pairs]
+        return RecvHandle([t for _, t in pairs], works, None)
 
 
 class MetaBoard:

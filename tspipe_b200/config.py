@@ -18,6 +18,9 @@ New optional keys (all defaulted so reference YAML files load unchanged):
 ``runtime.max_inflight``     batches the feeder may run ahead (default 3)
 ``runtime.prefetch``         stage-link receives posted ahead of need (default 2)
 ``runtime.peer_memory``      map peer GPUs' buffers for in-kernel NVLink reads (default True on CUDA)
+``runtime.peer_links``       stage-boundary tensors cross through peer-mapped ring buffers with copy engines instead of
+                            library send / receive kernels (default True; needs ``peer_memory``); ``runtime.link_slots``
+                            = messages in flight per link (default 4)
 ``runtime.placement``        ``colocated`` (teacher and student stage j share rank j) | ``split`` (teacher stages
                              on the first ranks of a replica, student stages on the rest; supervised mode)
 ``runtime.teacher_slots``    batches the split-placement teacher may run ahead (default 2)
@@ -49,7 +52,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True, "sm_reserve": None},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True, "sm_reserve": None, "peer_links": True, "link_slots": 4},
 }
 
 

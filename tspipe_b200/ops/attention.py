@@ -127,7 +127,7 @@ def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional
     lse = torch.empty((b * h, nq), dtype=torch.float32, device=q.device) if want_lse else None
     L = _f.lib()
     L.tsp_attn_fwd.restype = _c.c_int
-    with torch.cuda.device(q.device):
+    with _f.on_device(q.device):
         code = L.tsp_attn_fwd(_f._ptr(q), _f._ptr(k), _f._ptr(v), _f._ptr(o), _f._ptr(lse), _c.c_int(b), _c.c_int(h),
                               _c.c_int(nq), _c.c_int(nk), _c.c_int(d), _c.c_int(dv), _strides3(q), _strides3(k),
                               _strides3(v), _strides3(o), _c.c_float(scale),

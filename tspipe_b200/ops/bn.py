@@ -117,7 +117,7 @@ class _BnAct(torch.autograd.Function):
         save = torch.empty(segs * 2 * c, dtype=torch.float32, device=x.device)
         wf = weight.detach() if weight.dtype == torch.float32 else weight.detach().float()
         bf = bias.detach() if bias.dtype == torch.float32 else bias.detach().float()
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             st = _f._stream()
             if fixed is None and pre_sums is None:
                 _f._check(L.tsp_bn_stats(_f._ptr(x), _c.c_int64(m), _c.c_int(c), _c.c_int(dt), _f._ptr(sums),
@@ -149,7 +149,7 @@ class _BnAct(torch.autograd.Function):
         dres = torch.empty_like(x) if (ctx.has_res and ctx.relu) else None
         segs = ctx.segs
         sums = torch.empty(segs * 2 * c, dtype=torch.float32, device=x.device)
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             st = _f._stream()
             relu = _c.c_int(1 if ctx.relu else 0)
             _f._check(L.tsp_bn_bwd_reduce(_f._ptr(dy), _f._ptr(x), _f._ptr(y), _f._ptr(dres), _f._ptr(save),

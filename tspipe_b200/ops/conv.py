@@ -60,7 +60,7 @@ class _StemConv(torch.autograd.Function):
         wm = weight_matrix(weight)
         L = _f.lib()
         L.tsp_conv_stem_fwd.restype = _c.c_int
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             code = L.tsp_conv_stem_fwd(_f._ptr(x), _f._ptr(wm), _f._ptr(y), _f._ptr(sums), _c.c_int(n), _c.c_int(h),
                                        _c.c_int(w), _c.c_int(segs), _f._ptr(_gemm._status_word(x.device)), _f._stream())
         _f._check(code, "tsp_conv_stem_fwd")
@@ -118,6 +118,9 @@ def clear_weight_cache() -> None:
 def _w16(weight: torch.Tensor) -> torch.Tensor:
     """bf16 copy of a convolution weight laid out ``[Cout][kh][kw][Cin]`` (no copy beyond the cast when the
     parameter is stored channels-last, which is how the runtime keeps 4-D parameters)."""
+    if _f.IN_CAPTURE:                   # inside a CUDA graph the cast is part of the graph
+        w = weight.detach().to(torch.bfloat16).permute(0, 2, 3, 1)
+        return w if w.is_contiguous() else w.contiguous()
     hit = _W16.get(id(weight))
     if hit is not None and hit[0] is weight and hit[1] == weight._version and hit[2].device == weight.device:
         return hit[2]
@@ -191,7 +194,7 @@ class _Conv2d(torch.autograd.Function):
         w16 = _w16(weight)
         y = torch.empty((n, cout, ho, wo), dtype=torch.bfloat16, device=x.device, memory_format=torch.channels_last)
         sums = torch.zeros(segs * 2 * cout, dtype=torch.float32, device=x.device) if want_sums else None
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             code = _lib().tsp_conv_fprop(_f._ptr(x), _f._ptr(w16), _f._ptr(y), _f._ptr(sums), _c.c_int(segs), _c.c_int(n),
                                          _c.c_int(h), _c.c_int(w), _c.c_int(cin), _c.c_int(cout), _c.c_int(k),
                                          _c.c_int(stride), _f._ptr(_gemm._status_word(x.device)), _f._stream())
@@ -214,7 +217,7 @@ class _Conv2d(torch.autograd.Function):
         L = _lib()
         status = _f._ptr(_gemm._status_word(x.device))
         dx = dw = None
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             st = _f._stream()
             if ctx.needs_input_grad[0]:
                 dx = torch.empty_like(x)

@@ -51,7 +51,47 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return _c.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """Raw handle of the current stream of the current device (the launchers' last argument)."""
+    return _c.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
+
+
+IN_CAPTURE = 0          # > 0 while a stage is being recorded into a CUDA graph
+
+
+class capturing:
+    """While a stage is recorded into a CUDA graph the per-step caches of derived tensors (bf16 weight copies) are
+    bypassed: what the graph needs it must compute itself at every replay."""
+
+    def __enter__(self):
+        global IN_CAPTURE
+        IN_CAPTURE += 1
+        return self
+
+    def __exit__(self, *exc):
+        global IN_CAPTURE
+        IN_CAPTURE -= 1
+        return False
+
+
+class _Current:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_CURRENT = _Current()
+
+
+def on_device(device):
+    """``with on_device(t.device):`` makes the tensor's device current for the launches inside.  Free when it already
+    is (every launch of a training step: the executor thread and autograd's device thread both run with their device
+    current), so the per-launch cost of the general context manager is only paid when it does something."""
+    idx = device.index
+    if idx is None or torch._C._cuda_getDevice() == idx:
+        return _CURRENT
+    return torch.cuda.device(idx)
 
 
 def _check(code: int, what: str) -> None:
@@ -79,7 +119,7 @@ def ema_update_(teacher: torch.Tensor, student: torch.Tensor, momentum: float,
     assert teacher.is_contiguous() and student.is_contiguous() and teacher.numel() == student.numel()
     if teacher.numel() == 0:
         return
-    with torch.cuda.device(teacher.device):
+    with on_device(teacher.device):
         _check(lib().tsp_ema_update(_ptr(teacher), _ptr(student), _c.c_int64(teacher.numel()),
                                     _c.c_float(momentum), _ptr(bf16_shadow), _stream()), "tsp_ema_update")
     _count()
@@ -107,7 +147,7 @@ def build_chunks(offsets: Sequence[int], numels: Sequence[int], device, lo: int 
 @torch.no_grad()
 def lars_step_(p, g, mu, chunks, seg_hp, norms, grad_scale=1.0, teacher=None, ema_m=0.0) -> None:
     n_seg = seg_hp.shape[0]
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(lib().tsp_lars_step(_ptr(p), _ptr(g), _ptr(mu), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
                                    _c.c_float(grad_scale), _ptr(norms), _c.c_int(n_seg), _ptr(teacher),
                                    _c.c_int64(0 if teacher is None else teacher.numel()), _c.c_float(ema_m),
@@ -117,7 +157,7 @@ def lars_step_(p, g, mu, chunks, seg_hp, norms, grad_scale=1.0, teacher=None, em
 
 @torch.no_grad()
 def lars_norms_(p, g, chunks, seg_hp, norms, grad_scale=1.0) -> None:
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(lib().tsp_lars_norms(_ptr(p), _ptr(g), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
                                     _c.c_float(grad_scale), _ptr(norms), _c.c_int(seg_hp.shape[0]), _stream()),
                "tsp_lars_norms")
@@ -126,7 +166,7 @@ def lars_norms_(p, g, chunks, seg_hp, norms, grad_scale=1.0) -> None:
 
 @torch.no_grad()
 def lars_apply_(p, g, mu, chunks, seg_hp, norms, grad_scale=1.0, teacher=None, ema_m=0.0) -> None:
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(lib().tsp_lars_apply(_ptr(p), _ptr(g), _ptr(mu), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
                                     _c.c_float(grad_scale), _ptr(norms), _ptr(teacher),
                                     _c.c_int64(0 if teacher is None else teacher.numel()), _c.c_float(ema_m),
@@ -136,7 +176,7 @@ def lars_apply_(p, g, mu, chunks, seg_hp, norms, grad_scale=1.0, teacher=None, e
 
 @torch.no_grad()
 def adamw_step_(p, g, m, v, chunks, seg_hp, grad_scale=1.0, teacher=None, ema_m=0.0) -> None:
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(lib().tsp_adamw_step(_ptr(p), _ptr(g), _ptr(m), _ptr(v), _ptr(chunks), _c.c_int(chunks.shape[0]),
                                     _ptr(seg_hp), _c.c_float(grad_scale), _ptr(teacher),
                                     _c.c_int64(0 if teacher is None else teacher.numel()), _c.c_float(ema_m),
@@ -146,7 +186,7 @@ def adamw_step_(p, g, m, v, chunks, seg_hp, grad_scale=1.0, teacher=None, ema_m=
 
 @torch.no_grad()
 def sgd_step_(p, g, buf, chunks, seg_hp, grad_scale=1.0, teacher=None, ema_m=0.0) -> None:
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(lib().tsp_sgd_step(_ptr(p), _ptr(g), _ptr(buf), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
                                   _c.c_float(grad_scale), _ptr(teacher),
                                   _c.c_int64(0 if teacher is None else teacher.numel()), _c.c_float(ema_m), _stream()),
@@ -165,7 +205,7 @@ class _ByolPair(torch.autograd.Function):
         n, d = x.shape
         loss = torch.zeros((), dtype=torch.float32, device=x.device)
         gx = torch.empty_like(x)
-        with torch.cuda.device(x.device):
+        with on_device(x.device):
             _check(lib().tsp_byol_loss(_ptr(x), _ptr(y), _c.c_int(n), _c.c_int(d), _c.c_int(_dt(x)),
                                        _c.c_float(scale), _ptr(loss), _ptr(gx), _stream()), "tsp_byol_loss")
         _count()
@@ -202,7 +242,7 @@ class _KdCe(torch.autograd.Function):
         gs = torch.empty_like(s2)
         lab = None if labels is None else labels.reshape(-1).to(torch.int64).contiguous()
         msk = None if row_mask is None else row_mask.reshape(-1).to(torch.uint8).contiguous()
-        with torch.cuda.device(s.device):
+        with on_device(s.device):
             _check(lib().tsp_kd_ce_loss(_ptr(s2), _ptr(t2), _ptr(lab), _ptr(msk), _c.c_int(n), _c.c_int(c),
                                         _c.c_int(_dt(s2)), _c.c_int(0 if t2 is None else _dt(t2)), _c.c_float(temp),
                                         _c.c_float(w_ce), _c.c_float(w_kd), _ptr(loss), _ptr(gs), _stream()),
@@ -244,7 +284,7 @@ class _Cosine(torch.autograd.Function):
         loss = torch.zeros((), dtype=torch.float32, device=x.device)
         gx = torch.empty_like(x2)
         msk = None if row_mask is None else row_mask.reshape(-1).to(torch.uint8).contiguous()
-        with torch.cuda.device(x.device):
+        with on_device(x.device):
             _check(lib().tsp_cosine_loss(_ptr(x2), _ptr(y2), _ptr(msk), _c.c_int(n), _c.c_int(d), _c.c_int(_dt(x2)),
                                          _c.c_float(scale), _ptr(loss), _ptr(gx), _stream()), "tsp_cosine_loss")
         _count()
@@ -281,7 +321,7 @@ class _LayerNorm(torch.autograd.Function):
         mean = torch.empty(rows, dtype=torch.float32, device=x.device)
         rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         wf, bf = w.detach().float().contiguous(), b.detach().float().contiguous()
-        with torch.cuda.device(x.device):
+        with on_device(x.device):
             _check(lib().tsp_layernorm_fwd(_ptr(x2), _ptr(wf), _ptr(bf), _ptr(y), _ptr(mean), _ptr(rstd),
                                            _c.c_int(rows), _c.c_int(d), _c.c_float(eps), _c.c_int(_dt(x2)), _stream()),
                    "tsp_layernorm_fwd")
@@ -301,7 +341,7 @@ class _LayerNorm(torch.autograd.Function):
         db = torch.empty(d, dtype=torch.float32, device=x2.device)
         nb = lib().tsp_layernorm_bwd_blocks(_c.c_int(rows))
         partial = torch.empty(nb * 2 * d, dtype=torch.float32, device=x2.device)
-        with torch.cuda.device(x2.device):
+        with on_device(x2.device):
             _check(lib().tsp_layernorm_bwd(_ptr(dy2), _ptr(x2), _ptr(wf), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(dw),
                                            _ptr(db), _ptr(partial), _c.c_int(rows), _c.c_int(d), _c.c_int(_dt(x2)),
                                            _stream()), "tsp_layernorm_bwd")
@@ -323,7 +363,7 @@ class _Gelu(torch.autograd.Function):
         d = x.shape[-1]
         y = torch.empty_like(x)
         bf = None if bias is None else bias.detach().float().contiguous()
-        with torch.cuda.device(x.device):
+        with on_device(x.device):
             _check(lib().tsp_gelu_fwd(_ptr(x), _ptr(bf), _ptr(y), _c.c_int64(x.numel()), _c.c_int(d), _c.c_int(_dt(x)),
                                       _stream()), "tsp_gelu_fwd")
         _count()
@@ -338,7 +378,7 @@ class _Gelu(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty_like(x)
         d = x.shape[-1]
-        with torch.cuda.device(x.device):
+        with on_device(x.device):
             _check(lib().tsp_gelu_bwd(_ptr(dy), _ptr(x), _ptr(bf if ctx.has_bias else None), _ptr(dx),
                                       _c.c_int64(x.numel()), _c.c_int(d), _c.c_int(_dt(x)), _stream()), "tsp_gelu_bwd")
         _count()
@@ -361,7 +401,7 @@ def gelu(x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
 def dp_reduce_norms_(grad_ptrs, n_peers, scale, g_out, p, chunks, seg_hp, norms) -> None:
     L = lib()
     L.tsp_dp_reduce_norms.restype = _c.c_int
-    with torch.cuda.device(p.device):
+    with on_device(p.device):
         _check(L.tsp_dp_reduce_norms(grad_ptrs, _c.c_int(n_peers), _c.c_float(scale), _ptr(g_out), _ptr(p),
                                      _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp), _ptr(norms),
                                      _c.c_int(seg_hp.shape[0]), _stream()), "tsp_dp_reduce_norms")
@@ -373,7 +413,7 @@ def publish_norms_(table_ptrs, n_peers, self_idx, norms) -> None:
     """This rank's partial LARS norms into slot ``self_idx`` of every replica's table (peer stores)."""
     L = lib()
     L.tsp_publish_norms.restype = _c.c_int
-    with torch.cuda.device(norms.device):
+    with on_device(norms.device):
         _check(L.tsp_publish_norms(table_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _ptr(norms),
                                    _c.c_int(norms.numel()), _stream()), "tsp_publish_norms")
     _count()
@@ -384,7 +424,7 @@ def sum_norms_(table, n_peers, norms) -> None:
     """``norms = sum_r table[r]`` over the replicas' slots."""
     L = lib()
     L.tsp_sum_norms.restype = _c.c_int
-    with torch.cuda.device(norms.device):
+    with on_device(norms.device):
         _check(L.tsp_sum_norms(_ptr(table), _c.c_int(n_peers), _c.c_int(norms.numel()), _ptr(norms), _stream()),
                "tsp_sum_norms")
     _count()
@@ -394,7 +434,7 @@ def sum_norms_(table, n_peers, norms) -> None:
 def dp_lars_apply_(param_ptrs, n_peers, self_idx, g, mu, chunks, seg_hp, norms) -> None:
     L = lib()
     L.tsp_dp_lars_apply.restype = _c.c_int
-    with torch.cuda.device(g.device):
+    with on_device(g.device):
         _check(L.tsp_dp_lars_apply(param_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _ptr(g), _ptr(mu), _ptr(chunks),
                                    _c.c_int(chunks.shape[0]), _ptr(seg_hp), _ptr(norms), _stream()),
                "tsp_dp_lars_apply")
@@ -405,7 +445,7 @@ def dp_lars_apply_(param_ptrs, n_peers, self_idx, g, mu, chunks, seg_hp, norms) 
 def dp_adamw_step_(grad_ptrs, param_ptrs, n_peers, self_idx, scale, m, v, chunks, seg_hp) -> None:
     L = lib()
     L.tsp_dp_adamw_step.restype = _c.c_int
-    with torch.cuda.device(m.device):
+    with on_device(m.device):
         _check(L.tsp_dp_adamw_step(grad_ptrs, param_ptrs, _c.c_int(n_peers), _c.c_int(self_idx), _c.c_float(scale),
                                    _ptr(m), _ptr(v), _ptr(chunks), _c.c_int(chunks.shape[0]), _ptr(seg_hp),
                                    _stream()), "tsp_dp_adamw_step")

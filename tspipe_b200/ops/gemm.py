@@ -80,7 +80,7 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = N
     L = _f.lib()
     fn = L.tsp_gemm_bf16_tn_2cta if (_two_cta if two_cta is None else two_cta) else L.tsp_gemm_bf16_tn
     fn.restype = _c.c_int
-    with torch.cuda.device(a.device):
+    with _f.on_device(a.device):
         code = fn(_f._ptr(a), _f._ptr(b), _f._ptr(c), _f._ptr(bf), _c.c_int(m), _c.c_int(n), _c.c_int(k),
                   _c.c_int(k), _c.c_int(k), _c.c_int(n), _c.c_int(_f._dt(c)), _c.c_int(epi),
                   _f._ptr(_status_word(a.device)), _f._stream())
@@ -106,6 +106,8 @@ def _w16(weight: torch.Tensor) -> torch.Tensor:
     base = weight._base if weight._base is not None else weight
     if not base.is_contiguous() or base.dtype == torch.bfloat16:
         return weight.detach().to(torch.bfloat16).contiguous()
+    if _f.IN_CAPTURE:                   # inside a CUDA graph the cast is part of the graph
+        return weight.detach().to(torch.bfloat16).contiguous()
     hit = _W16.get(id(base))
     if hit is None or hit[0] is not base or hit[1] != base._version:
         hit = (base, base._version, base.detach().to(torch.bfloat16))
@@ -122,6 +124,8 @@ _W16T = {}       # id(parameter slice base) -> (weight, version, bf16 transposed
 def _w16_t(weight: torch.Tensor) -> torch.Tensor:
     """bf16 ``weight.T`` as a contiguous ``[K, N]`` matrix (the B operand of ``dX = dY @ W`` on the ``A @ B^T`` GEMM),
     made once per weight and optimizer step."""
+    if _f.IN_CAPTURE:
+        return weight.detach().to(torch.bfloat16).t().contiguous()
     base = weight._base if weight._base is not None else weight
     key = (id(base), weight.storage_offset(), tuple(weight.shape))
     hit = _W16T.get(key)
@@ -139,7 +143,7 @@ def _column_sums(dy2: torch.Tensor) -> torch.Tensor:
     sums = torch.empty(2 * n, dtype=torch.float32, device=dy2.device)
     L = _f.lib()
     L.tsp_bn_stats.restype = _c.c_int
-    with torch.cuda.device(dy2.device):
+    with _f.on_device(dy2.device):
         _f._check(L.tsp_bn_stats(_f._ptr(dy2), _c.c_int64(m), _c.c_int(n), _c.c_int(_f._dt(dy2)), _f._ptr(sums),
                                  _c.c_int(1), _f._stream()), "tsp_bn_stats")
     _f._count(2)
@@ -177,7 +181,7 @@ class _Linear(torch.autograd.Function):
         status = _f._ptr(_status_word(x2.device))
         dims = (_c.c_int(m), _c.c_int(1), _c.c_int(1), _c.c_int(k), _c.c_int(n), _c.c_int(1), _c.c_int(1))
         dx = dw = db = None
-        with torch.cuda.device(x2.device):
+        with _f.on_device(x2.device):
             st = _f._stream()
             if ctx.needs_input_grad[0]:
                 if _DX_ON_PAIR_GEMM:
@@ -243,7 +247,7 @@ def matmul_nt_gathered(a: torch.Tensor, b_sources, rows_per_b: int, out_dtype: t
     c = torch.empty(m, r * rows_per_b, dtype=out_dtype, device=a.device)
     L = _f.lib()
     L.tsp_gemm_bf16_tn_gathered_b.restype = _c.c_int
-    with torch.cuda.device(a.device):
+    with _f.on_device(a.device):
         code = L.tsp_gemm_bf16_tn_gathered_b(_f._ptr(a), pointer_table(b_sources), _c.c_int(r), _c.c_int(rows_per_b),
                                              _f._ptr(c), _c.c_int(m), _c.c_int(k), _c.c_int(k), _c.c_int(k),
                                              _c.c_int(r * rows_per_b), _c.c_int(_f._dt(c)),
@@ -340,7 +344,7 @@ class _FusedNCEGathered(torch.autograd.Function):
         lse = torch.empty(n, dtype=torch.float32, device=qn.device)
         L = _f.lib()
         L.tsp_attn_nce_gathered.restype = _c.c_int
-        with torch.cuda.device(qn.device):
+        with _f.on_device(qn.device):
             code = L.tsp_attn_nce_gathered(_f._ptr(q16), pointer_table(views), _c.c_int(len(views)), _c.c_int(n),
                                            _f._ptr(o), _f._ptr(lse), _c.c_int(n), _c.c_float(1.0 / temp),
                                            _c.c_float(1.0 / temp), _f._ptr(_status_word(qn.device)), _f._stream())

@@ -20,7 +20,7 @@ class _MaxPool(torch.autograd.Function):
         idx = torch.empty((n, ho, wo, c), dtype=torch.uint8, device=x.device) if need_idx else None
         L = _f.lib()
         L.tsp_maxpool3x3s2_fwd.restype = _c.c_int
-        with torch.cuda.device(x.device):
+        with _f.on_device(x.device):
             _f._check(L.tsp_maxpool3x3s2_fwd(_f._ptr(x), _f._ptr(y), _f._ptr(idx), _c.c_int(n), _c.c_int(h), _c.c_int(w),
                                              _c.c_int(c), _c.c_int(_f._dt(x)), _f._stream()), "tsp_maxpool3x3s2_fwd")
         _f._count()
@@ -37,7 +37,7 @@ class _MaxPool(torch.autograd.Function):
         dx = torch.empty((n, c, h, w), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
         L = _f.lib()
         L.tsp_maxpool3x3s2_bwd.restype = _c.c_int
-        with torch.cuda.device(dy.device):
+        with _f.on_device(dy.device):
             _f._check(L.tsp_maxpool3x3s2_bwd(_f._ptr(dy), _f._ptr(idx), _f._ptr(dx), _c.c_int(n), _c.c_int(h), _c.c_int(w),
                                              _c.c_int(c), _c.c_int(_f._dt(dy)), _f._stream()), "tsp_maxpool3x3s2_bwd")
         _f._count()

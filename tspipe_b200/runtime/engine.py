@@ -35,6 +35,7 @@ from torch import nn
 
 from ..batch_ops import Batch, ScatterGatherFn, defaultScatterGatherFn
 from ..comm.links import Link, MetaBoard, RecvHandle
+from ..comm.peer_link import make_link
 from ..comm.topology import Topology
 from ..logger import Log
 from ..schedule import Op, OpKind, ScheduleSpec, batch_block
@@ -199,6 +200,7 @@ class _Stored:
     outputs: List[Any]                # per nano: flat output leaves (with graph)
     grad_in_idx: List[int]            # indices of input leaves that carry a gradient upstream
     grad_out_idx: List[int]           # indices of output leaves that require grad
+    graph: Any = None                 # the CUDA-graph slot that ran the forward (its backward is a replay too)
 
 
 class StageEngine:
@@ -277,10 +279,24 @@ class StageEngine:
         else:
             self.compute = self.copy_stream = self.dp_stream = None
         j = topo.stage
-        self.fwd_in = Link(topo.fwd_groups[j - 1], topo.prev_rank, self.device) if not topo.is_first else None
-        self.bwd_out = Link(topo.bwd_groups[j - 1], topo.prev_rank, self.device) if not topo.is_first else None
-        self.fwd_out = Link(topo.fwd_groups[j], topo.next_rank, self.device) if not topo.is_last else None
-        self.bwd_in = Link(topo.bwd_groups[j], topo.next_rank, self.device) if not topo.is_last else None
+        rt = self.cfg["runtime"]
+
+        def link(groups, boundary: int, peer_rank: int, tag: str):
+            # activations and gradients cross a stage boundary through peer memory (copy engines) when both GPUs are
+            # in this node; the torch.distributed link otherwise
+            peer_dev = (self.device.index + peer_rank - topo.rank) if self.cuda else None
+            if peer_dev is not None and not 0 <= peer_dev < torch.cuda.device_count():
+                peer_dev = None
+            return make_link(groups[boundary], peer_rank, self.device, store=topo.store,
+                             name=f"plink/r{topo.replica}/{tag}{boundary}", peer_device=peer_dev,
+                             use_peer=bool(rt.get("peer_links", True)) and bool(rt.get("peer_memory", True)),
+                             slots=int(rt.get("link_slots", 4)), channels_last=self.channels_last and self.cuda,
+                             limit_ms=int(min(max(float(rt["timeout_s"]), 1.0), 600.0) * 1000))
+
+        self.fwd_in = link(topo.fwd_groups, j - 1, topo.prev_rank, "f") if not topo.is_first else None
+        self.bwd_out = link(topo.bwd_groups, j - 1, topo.prev_rank, "b") if not topo.is_first else None
+        self.fwd_out = link(topo.fwd_groups, j, topo.next_rank, "f") if not topo.is_last else None
+        self.bwd_in = link(topo.bwd_groups, j, topo.next_rank, "b") if not topo.is_last else None
         self.meta = MetaBoard(topo.store, topo.replica)
 
         # run-time state -------------------------------------------------------------------------
@@ -303,6 +319,12 @@ class StageEngine:
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
         self._teacher_graphs: Dict[Any, Any] = {}
+        self._graph_stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.student_graphs = None
+        if (self.cuda and self.cfg["runtime"].get("cuda_graphs", False) and self.S == 1
+                and self.cfg["runtime"].get("student_graphs", True) and self.flat_online.grad is not None):
+            from .stage_graph import StudentStageGraphs
+            self.student_graphs = StudentStageGraphs(self.online, self.flat_online, self.autocast, self.device)
         self.async_emu = bool(config["async_param_update_emulation"]["enabled"]) and not gp["enabled"]
         self._alt_params = None
         self._initial_params = self.flat_online.data.clone() if self.async_emu else None
@@ -379,6 +401,10 @@ class StageEngine:
                     continue
                 lo, hi = self.topo.rank_of(self.topo.replica, j), self.topo.rank_of(self.topo.replica, j + 1)
                 src, dst = (lo, hi) if down else (hi, lo)
+                mine = ((self.fwd_out if down else self.bwd_in) if self.topo.rank == lo
+                        else (self.fwd_in if down else self.bwd_out))
+                if not isinstance(mine, Link):
+                    continue                    # a peer-memory link: no communicator behind it
                 t = torch.zeros(1, device=self.device)
                 if self.topo.rank == src:
                     dist.send(t, dst, group=groups[j])
@@ -749,13 +775,18 @@ class StageEngine:
                     x = pt.unflatten(leaves, tree, wrapped)
                 if self.channels_last:
                     x = pt.tree_map_tensors(_to_channels_last, x)
+                slot = None
                 with _bn_segments(2 if merged else 1):
                     if teacher:
                         y = self._teacher_forward(module, x)
                         self.bn_group_target.step(2 if merged else 1)
                     else:
-                        with self._amp():
-                            y = module(x)
+                        y = None
+                        if self.student_graphs is not None:
+                            y, slot = self.student_graphs.forward((op.view, op.ub), x, 2 if merged else 1)
+                        if slot is None:
+                            with self._amp():
+                                y = module(x)
                         self.bn_group_online.step(2 if merged else 1)
                 outs.append(y)
                 if not teacher:
@@ -765,7 +796,7 @@ class StageEngine:
                     stored_in.append(leaves)
                     stored_out.append(oleaves)
             if not teacher:
-                self.acts[(op.batch, op.view, op.ub)] = _Stored(stored_in, stored_out, gin_idx, gout_idx)
+                self.acts[(op.batch, op.view, op.ub)] = _Stored(stored_in, stored_out, gin_idx, gout_idx, slot)
             if merged and last:
                 # the loss sees the two views as two outputs again (halves of the stacked batch)
                 for v in (0, 1):
@@ -811,11 +842,13 @@ class StageEngine:
             static_leaves = [l.clone() if isinstance(l, torch.Tensor) else l for l in leaves]
             static_in = pt.unflatten(static_leaves, tree, wrapped)
             graph = torch.cuda.CUDAGraph()
-            torch.cuda.current_stream().synchronize()
-            with torch.cuda.graph(graph):
+            from .stage_graph import capture
+
+            def body():
                 with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=self.autocast,
                                                      cache_enabled=False):
-                    static_out = module(static_in)
+                    return module(static_in)
+            static_out = capture(graph, self._graph_stream, None, body)
             entry = (2, graph, static_leaves, static_out)
             self._teacher_graphs[key] = entry
             # the capture itself did not execute anything: fall through to a replay
@@ -913,14 +946,19 @@ class StageEngine:
                 grads = self.out_grads.pop((b, v, k))
             else:
                 grads = self._recv_backward(op)
-            if outs:
-                torch.autograd.backward(outs, grads)
-            if not self.topo.is_first:
-                gin = []
-                for i in st.grad_in_idx:
-                    leaf = st.inputs[piece][i]
-                    gin.append(leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
-                self.bwd_out.send(gin)
+            if st.graph is not None:
+                gin = self.student_graphs.backward(st.graph, grads)
+                if not self.topo.is_first:
+                    self.bwd_out.send(gin)
+            else:
+                if outs:
+                    torch.autograd.backward(outs, grads)
+                if not self.topo.is_first:
+                    gin = []
+                    for i in st.grad_in_idx:
+                        leaf = st.inputs[piece][i]
+                        gin.append(leaf.grad if leaf.grad is not None else torch.zeros_like(leaf))
+                    self.bwd_out.send(gin)
             st.outputs[piece] = None
             st.inputs[piece] = None
             if all(o is None for o in st.outputs):
@@ -1033,6 +1071,9 @@ class StageEngine:
     # -- retire / drain ------------------------------------------------------------------------------
     def _retire(self, b: int) -> None:
         self.feeds.pop(b - 1, None)
+        for link in (self.fwd_in, self.fwd_out, self.bwd_in, self.bwd_out):
+            if link is not None and hasattr(link, "poll"):
+                link.poll()                 # a device-side wait of a peer link that gave up surfaces here
         if self.on_batch_done is not None:
             self.on_batch_done(b)
 
@@ -1042,6 +1083,9 @@ class StageEngine:
                 link.flush()
         if self.cuda:
             self.compute.synchronize()
+        for link in (self.fwd_in, self.bwd_in):
+            if link is not None and hasattr(link, "poll"):
+                link.poll(sync=True)
 
 
 def _bn_segments(n: int):
