@@ -77,7 +77,10 @@ def parse(argv=None):
                    help="reference arm: as shipped (fp32), under bf16 autocast, or both")
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--cuda-graphs", action="store_true", help="replay teacher stage forwards from CUDA graphs")
+    p.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false",
+                   help="run every stage eagerly instead of replaying stage forwards / backwards from CUDA graphs")
+    p.add_argument("--cuda-graphs", dest="cuda_graphs", action="store_true", help=argparse.SUPPRESS)
+    p.set_defaults(cuda_graphs=True)
     p.add_argument("--no-pipeline", action="store_true", help="skip the secondary pipelined-grid measurements")
     p.add_argument("--image", type=int, default=224)
     p.add_argument("--seq-len", type=int, default=512)
@@ -279,7 +282,7 @@ def measure(a, pp, dp, ub, split, e2e, placement="colocated"):
         on_split, tg_split = ([int(x) for x in part.split(",")] for part in a.split.split("/"))
     cfg = {"model_split": {"online": on_split, "target": tg_split},
            "runtime": {"num_ubatch": ub, "bwd_split": split, "dp_replicas": dp, "dtype": a.dtype,
-                       "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 300,
+                       "fused": not a.no_fused, "channels_last": True, "max_inflight": 3, "timeout_s": 120,
                        "peer_memory": not a.no_peer, "cuda_graphs": a.cuda_graphs, "placement": placement,
                        "dp_signals": not a.no_dp_signals, "dp_early_reduce": not a.no_dp_early,
                        "merge_views": not a.no_merge_views, "sm_reserve": None if a.sm_reserve < 0 else a.sm_reserve},
@@ -415,7 +418,7 @@ def pipeline_grids(world: int, workload: str):
     if world >= 2:
         grids.append((world, 1, world))              # one pipeline over all GPUs, N microbatches
     if world >= 4:
-        grids.append((2, world // 2, 1))
+        grids.append((2, world // 2, 2))
     if world >= 8:
         grids.append((4, world // 4, 2))
     return grids

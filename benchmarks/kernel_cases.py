@@ -321,6 +321,67 @@ def case_conv1():
           f"bwd {t_lb:.1f} us")
 
 
+def case_dp():
+    """Fused data-parallel LARS over peer memory, launched by torchrun on R GPUs: device time of the reduce-scatter +
+    norms kernel and of the update + all-gather kernel on a ResNet-50-sized flat buffer (max over ranks), with the bytes
+    each moves over NVLink.  ``dp [N_PARAMS_M]``."""
+    import os
+    import torch.distributed as dist
+    from torch import nn
+    from tspipe_b200.comm import peer
+    from tspipe_b200.comm.signals import SignalPad
+    from tspipe_b200.optim import LARS
+    from tspipe_b200.runtime.state import FlatParams
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    n_m = float(sys.argv[2]) if len(sys.argv) > 2 else 25.6
+    torch.manual_seed(0)
+    n_tensors = 160
+    each = int(n_m * 1e6 / n_tensors) // 64 * 64
+    params = [nn.Parameter(torch.randn(each, device=dev) * 0.05) for _ in range(n_tensors)]
+    flat = FlatParams(params, dev, with_grad=True, pad_to=world)
+    opt = LARS(params, lr=0.1, weight_decay=1e-6, momentum=0.9)
+    opt.bind_flat(flat, use_kernel=True)
+    ranks = list(range(world))
+    grads = peer.exchange(flat.grad, dist.group.WORLD, ranks)
+    datas = peer.exchange(flat.data, dist.group.WORLD, ranks)
+    opt.enable_dp(dist.group.WORLD, grads, datas, rank)
+    pad = SignalPad(dist.group.WORLD, ranks, rank, dev, limit_ms=20000)
+    table = torch.zeros(world * 2 * n_tensors, dtype=torch.float32, device=dev)
+    opt.enable_signals(pad, peer.exchange(table, dist.group.WORLD, ranks))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    t_red, t_step = [], []
+    for it in range(13):
+        flat.grad.normal_()
+        flush.zero_()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        opt.dp_reduce()
+        e[1].record()
+        opt.step()
+        e[2].record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            t_red.append(e[0].elapsed_time(e[1]) * 1e3)
+            t_step.append(e[1].elapsed_time(e[2]) * 1e3)
+    pad.check()
+    t = torch.tensor([sorted(t_red)[len(t_red) // 2], sorted(t_step)[len(t_step) // 2]], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        total = flat.total * 4
+        link = total * (world - 1) / world / world        # bytes one GPU pulls in (reduce) or pushes out (gather)
+        print(f"dp LARS over {world} GPUs, {flat.total / 1e6:.1f} M fp32 parameters: reduce-scatter + norms "
+              f"{float(t[0]):.1f} us, update + all-gather {float(t[1]):.1f} us (median of 10, max over ranks, includes "
+              f"the signal waits); NVLink bytes per GPU and kernel {link / 1e6:.1f} MB = {link / 770e9 * 1e6:.1f} us at "
+              f"770 GB/s; local HBM bytes of the shard {(total / world) * 5 / 1e6:.1f} MB")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     {"bn": case_bn, "bn_r50": case_bn_r50, "stem": case_stem, "lars": case_lars, "ema": case_ema, "kd": case_kd, "ln": case_ln, "gemm": case_gemm,
-     "infonce": case_infonce, "attn": case_attn, "conv": case_conv, "conv1": case_conv1}[sys.argv[1]]()
+     "infonce": case_infonce, "attn": case_attn, "conv": case_conv, "conv1": case_conv1, "dp": case_dp}[sys.argv[1]]()

@@ -28,7 +28,9 @@ New optional keys (all defaulted so reference YAML files load unchanged):
 ``runtime.fuse_ema``         fold the momentum-teacher update into the optimizer kernel when both are cut alike
 ``runtime.merge_views``      single stage, one microbatch: run both views of a network as one stacked forward /
                              backward with per-view BatchNorm statistics (default True)
-``runtime.cuda_graphs``      replay the teacher's stage forward from a CUDA graph (default False)
+``runtime.cuda_graphs``      replay stage forwards (teacher and student) and the student's stage backward from CUDA
+                             graphs, one pair per microbatch slot, after two eager calls (default True; stages with
+                             dropout, skip connections or host-side state run eagerly)
 ``runtime.dp_signals``       order the fused data-parallel kernels with device-side signal words in peer memory
                              (bounded waits) instead of tiny NCCL collectives (default True)
 ``runtime.dp_early_reduce``  start the data-parallel gradient reduction on a side stream right after the backward
@@ -52,7 +54,7 @@ DEFAULTS: Dict[str, Any] = {
     "async_param_update_emulation": {"enabled": False},
     "runtime": {"num_ubatch": None, "bwd_split": 2, "dp_replicas": None, "dtype": "fp32", "backend": "auto",
                 "fused": True, "channels_last": False, "max_inflight": 3, "resume": "",
-                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": False, "merge_views": True, "dp_signals": True, "dp_early_reduce": True, "sm_reserve": None, "peer_links": True, "link_slots": 4},
+                "prefetch": 2, "peer_memory": True, "fuse_ema": True, "placement": "colocated", "teacher_slots": 2, "heartbeat_s": 2.0, "timeout_s": 600.0, "cuda_graphs": True, "merge_views": True, "dp_signals": True, "dp_early_reduce": True, "sm_reserve": None, "peer_links": True, "link_slots": 4},
 }
 
 

@@ -230,7 +230,7 @@ class _Conv2d(torch.autograd.Function):
                 # The kernel ADDS into its output.  When the parameter's gradient already lives in an fp32 buffer of
                 # the kernel's layout ([Cout][k][k][Cin], i.e. channels-last, as in the runtime's flat gradient
                 # buffer) the sum goes straight there and autograd gets nothing more to accumulate.
-                g = weight.grad
+                g = weight.grad if weight.is_leaf else None
                 if (_ACCUMULATE_IN_PLACE and g is not None and g.dtype == torch.float32 and g.shape == weight.shape
                         and g.permute(0, 2, 3, 1).is_contiguous()):
                     target = g

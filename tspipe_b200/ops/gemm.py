@@ -195,7 +195,7 @@ class _Linear(torch.autograd.Function):
                 if ctx.dtypes[0] != torch.bfloat16:
                     dx = dx.to(ctx.dtypes[0])
             if ctx.needs_input_grad[1]:
-                g = weight.grad
+                g = weight.grad if weight.is_leaf else None
                 if (_conv._ACCUMULATE_IN_PLACE and g is not None and g.dtype == torch.float32 and g.is_contiguous()
                         and g.shape == weight.shape):
                     target = g                     # the kernel adds into the existing gradient buffer

@@ -319,15 +319,16 @@ class StageEngine:
         self.on_flushed: Optional[Callable[[int], None]] = None
         self.steps_done = 0
         self._teacher_graphs: Dict[Any, Any] = {}
+        self._teacher_graph_launches: Dict[Any, int] = {}
         self._graph_stream = torch.cuda.Stream(self.device) if self.cuda else None
-        self.student_graphs = None
-        if (self.cuda and self.cfg["runtime"].get("cuda_graphs", False) and self.S == 1
-                and self.cfg["runtime"].get("student_graphs", True) and self.flat_online.grad is not None):
-            from .stage_graph import StudentStageGraphs
-            self.student_graphs = StudentStageGraphs(self.online, self.flat_online, self.autocast, self.device)
         self.async_emu = bool(config["async_param_update_emulation"]["enabled"]) and not gp["enabled"]
         self._alt_params = None
         self._initial_params = self.flat_online.data.clone() if self.async_emu else None
+        self.student_graphs = None
+        if (self.cuda and self.cfg["runtime"].get("cuda_graphs", False) and self.S == 1 and not self.async_emu
+                and self.cfg["runtime"].get("student_graphs", True) and self.flat_online.grad is not None):
+            from .stage_graph import StudentStageGraphs
+            self.student_graphs = StudentStageGraphs(self.online, self.flat_online, self.autocast, self.device)
         self.watchdog = None
         self._amp_open = False
         self.error: Optional[BaseException] = None
@@ -848,7 +849,11 @@ class StageEngine:
                 with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=self.autocast,
                                                      cache_enabled=False):
                     return module(static_in)
+            from ..ops import fused as _fused
+            n0 = _fused.LAUNCHES
             static_out = capture(graph, self._graph_stream, None, body)
+            self._teacher_graph_launches[key] = _fused.LAUNCHES - n0
+            _fused.LAUNCHES = n0
             entry = (2, graph, static_leaves, static_out)
             self._teacher_graphs[key] = entry
             # the capture itself did not execute anything: fall through to a replay
@@ -856,6 +861,8 @@ class StageEngine:
         for i in tpos:
             static_leaves[i].copy_(leaves[i])
         graph.replay()
+        from ..ops import fused as _fused
+        _fused._count(self._teacher_graph_launches.get(key, 0))
         return pt.tree_map_tensors(lambda t: t.clone(), static_out)
 
     def _send_forward(self, op: Op, teacher: bool, outs: List[Any]) -> None:
