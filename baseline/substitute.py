@@ -56,7 +56,7 @@ def _bert(torch, nn, layers, hidden=768, heads=12, ffn=3072, vocab=30522, max_po
     class Bert(nn.Module):
         def __init__(self):
             super().__init__()
-            self.word, self.posn, self.type = nn.Embedding(vocab, hidden), nn.Embedding(max_pos, hidden), nn.Embedding(2, hidden)
+            self.word, self.posn, self.seg = nn.Embedding(vocab, hidden), nn.Embedding(max_pos, hidden), nn.Embedding(2, hidden)
             self.emb_norm = nn.LayerNorm(hidden, eps=1e-12)
             layer = nn.TransformerEncoderLayer(hidden, heads, ffn, dropout=0.0, activation="gelu", batch_first=True,
                                                norm_first=False)
@@ -66,7 +66,7 @@ def _bert(torch, nn, layers, hidden=768, heads=12, ffn=3072, vocab=30522, max_po
 
         def forward(self, ids):
             pos = torch.arange(ids.shape[1], device=ids.device)
-            h = self.emb_norm(self.word(ids) + self.posn(pos)[None] + self.type.weight[0])
+            h = self.emb_norm(self.word(ids) + self.posn(pos)[None] + self.seg.weight[0])
             h = self.enc(h)
             z = self.head_norm(torch.nn.functional.gelu(self.dense(h)))
             return torch.nn.functional.linear(z, self.word.weight, self.bias), h

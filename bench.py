@@ -420,7 +420,7 @@ def pipeline_grids(world: int, workload: str):
     if world >= 4:
         grids.append((2, world // 2, 2))
     if world >= 8:
-        grids.append((4, world // 4, 2))
+        grids.append((4, world // 4, 4))
     return grids
 
 
@@ -485,9 +485,14 @@ def run_ours(a):
         # the same job on the pipelined grids that fit this GPU count
         plist = []
         for gpp, gdp, gub in pipeline_grids(world, a.workload):
-            p2 = measure(a, gpp, gdp, gub, split, e2e=False)
-            plist.append({k: p2[k] for k in ("value", "ms_per_step", "parallelism", "microbatches", "gpu_launches",
-                                             "device_ms_per_step_by_op")})
+            try:
+                p2 = measure(a, gpp, gdp, gub, split, e2e=False)
+                plist.append({k: p2[k] for k in ("value", "ms_per_step", "parallelism", "microbatches",
+                                                 "gpu_launches", "device_ms_per_step_by_op")})
+            except Exception as e:  # noqa: BLE001 - the headline above stands on its own
+                plist.append({"parallelism": f"dp{gdp}xpp{gpp}", "microbatches": gub,
+                              "error": f"{type(e).__name__}: {e}"[:300]})
+                break
         if plist:
             out["pipeline"] = plist
     if rank == 0:

@@ -14,7 +14,6 @@ import argparse
 import ast
 import os
 import sys
-import time
 
 import torch
 import yaml
@@ -27,6 +26,7 @@ from tspipe_b200.losses import byol_loss, ema_update  # noqa: E402
 from tspipe_b200.models.resnet import byol_networks  # noqa: E402
 from tspipe_b200.optim import LARS, SGD, AdamW  # noqa: E402
 from tspipe_b200.profiler import TSPipeProfiler  # noqa: E402
+from tspipe_b200.run_log import RunLog  # noqa: E402
 from tspipe_b200.schedules import cosine_lr, cosine_momentum  # noqa: E402
 
 
@@ -59,21 +59,31 @@ def main() -> None:
             loader = FastDataLoader(two_crop_imagefolder(cfg["dataset"]["path"], cfg["dataset"]["name"]), batch_size=bs,
                                     num_workers=cfg["trainer"]["num_workers"], shuffle=True, drop_last=True)
         base_lr = optimizer.param_groups[0]["lr"]
-        niter, t0 = 0, time.time()
+        log = RunLog(args.artifact_dir, enabled=tsp.is_primary())      # TensorBoard scalars + scalars.csv + model.pth
+        niter = 0
         for epoch in range(epochs):
             for (v1, v2), _ in loader:
                 loss = tsp.feed(v1, v2)
                 niter += 1
-                if loss is not None and niter % 10 == 0 and tsp.is_primary():
-                    print(f"iter {niter} loss {loss:.4f} {niter * bs / (time.time() - t0):.1f} img/s", flush=True)
+                if loss is not None:
+                    log.scalar("loss", loss, niter)
+                    if niter % 10 == 0 and tsp.is_primary():
+                        print(f"iter {niter} loss {loss:.4f} {tsp.meter.recent():.1f} img/s", flush=True)
                 if args.max_iters and niter >= args.max_iters:
                     break
             tsp.feed_epoch()
-            tsp.update_lr(cosine_lr(epoch + 1, epochs, base_lr))
-            tsp.update_momentum(cosine_momentum(epoch, epochs, m0))
+            lr, m = cosine_lr(epoch + 1, epochs, base_lr), cosine_momentum(epoch, epochs, m0)
+            tsp.update_lr(lr)
+            tsp.update_momentum(m)
+            log.scalar("learning_rate", lr, niter)
+            log.scalar("momentum", m, niter)
+            log.scalar("images_per_second", tsp.meter.overall(), niter)
             if args.max_iters and niter >= args.max_iters:
                 break
-        tsp.stop()
+        for k, loss in enumerate(tsp.stop()):        # losses of the batches still in flight
+            log.scalar("loss", loss, niter + 1 + k)
+        log.save_final(tsp, optimizer)           # model.pth: online / target / optimizer state dicts
+        log.close()
 
 
 if __name__ == "__main__":

@@ -14,7 +14,6 @@ from __future__ import annotations
 import argparse
 import os
 import sys
-import time
 from argparse import Namespace
 
 import torch
@@ -26,6 +25,7 @@ from tspipe_b200.batch_ops import Batch  # noqa: E402
 from tspipe_b200.losses import distil_loss  # noqa: E402
 from tspipe_b200.models import bert as B  # noqa: E402
 from tspipe_b200.optim import AdamW  # noqa: E402
+from tspipe_b200.run_log import RunLog  # noqa: E402
 from tspipe_b200.schedules import linear_warmup_decay  # noqa: E402
 from tspipe_b200.utils import pytree as pt  # noqa: E402
 
@@ -83,7 +83,7 @@ def main() -> None:
                                       alpha_cos=args.alpha_cos))
     g = torch.Generator().manual_seed(0)
     seq = min(args.seq_len, tcfg.max_pos)
-    t0 = time.time()
+    log = RunLog(args.artifact_dir, enabled=tsp.is_primary())      # TensorBoard scalars + scalars.csv + model.pth
     for it in range(args.iters):
         ids = torch.randint(1000 if tcfg.vocab_size > 2000 else 4, tcfg.vocab_size, (args.batch_size, seq), generator=g)
         attn = torch.ones_like(ids)
@@ -92,9 +92,15 @@ def main() -> None:
         counts = (int((labels >= 0).sum()), int(attn.sum()))
         tsp.update_lr(linear_warmup_decay(it, args.iters, args.lr, int(args.warmup_prop * args.iters)))
         loss = tsp.feed(batch, batch, (labels, attn) + counts)
-        if loss is not None and (it + 1) % 10 == 0 and tsp.is_primary():
-            print(f"iter {it + 1} loss {loss:.4f} {(it + 1) * args.batch_size / (time.time() - t0):.1f} samples/s", flush=True)
-    tsp.stop()
+        if loss is not None:
+            log.scalar("loss", loss, it + 1)
+            if (it + 1) % 10 == 0 and tsp.is_primary():
+                print(f"iter {it + 1} loss {loss:.4f} {tsp.meter.recent():.1f} samples/s", flush=True)
+    for k, loss in enumerate(tsp.stop()):
+        log.scalar("loss", loss, args.iters + 1 + k)
+    log.scalar("samples_per_second", tsp.meter.overall(), args.iters)
+    log.save_final(tsp, opt)
+    log.close()
 
 
 if __name__ == "__main__":

@@ -373,7 +373,7 @@ def case_dp():
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         total = flat.total * 4
-        link = total * (world - 1) / world / world        # bytes one GPU pulls in (reduce) or pushes out (gather)
+        link = total / world * (world - 1)                # bytes one GPU pulls in (reduce) or pushes out (gather)
         print(f"dp LARS over {world} GPUs, {flat.total / 1e6:.1f} M fp32 parameters: reduce-scatter + norms "
               f"{float(t[0]):.1f} us, update + all-gather {float(t[1]):.1f} us (median of 10, max over ranks, includes "
               f"the signal waits); NVLink bytes per GPU and kernel {link / 1e6:.1f} MB = {link / 770e9 * 1e6:.1f} us at "

@@ -17,7 +17,6 @@ import argparse
 import math
 import os
 import sys
-import time
 from argparse import Namespace
 
 import torch
@@ -29,6 +28,7 @@ from tspipe_b200.dataloader import DummyInputGenerator, FastDataLoader  # noqa: 
 from tspipe_b200.losses import ema_update, moco_loss  # noqa: E402
 from tspipe_b200.models.vit import moco_vit_networks  # noqa: E402
 from tspipe_b200.optim import LARS, AdamW  # noqa: E402
+from tspipe_b200.run_log import RunLog  # noqa: E402
 
 
 def main() -> None:
@@ -67,7 +67,8 @@ def main() -> None:
         loader = FastDataLoader(two_crop_imagefolder(args.data), batch_size=args.batch_size, shuffle=True,
                                 num_workers=16, drop_last=True)
     iters_per_epoch = len(loader)
-    niter, t0 = 0, time.time()
+    log = RunLog(args.artifact_dir, enabled=tsp.is_primary())      # TensorBoard scalars + scalars.csv + model.pth
+    niter = 0
     for epoch in range(args.epochs):
         for i, ((v1, v2), _) in enumerate(loader):
             e = epoch + i / iters_per_epoch
@@ -81,14 +82,21 @@ def main() -> None:
                 tsp.update_momentum(1 - 0.5 * (1 + math.cos(math.pi * e / args.epochs)) * (1 - args.moco_m))
             loss = tsp.feed(v1, v2)
             niter += 1
-            if loss is not None and niter % 10 == 0 and tsp.is_primary():
-                print(f"iter {niter} loss {loss:.4f} {niter * args.batch_size / (time.time() - t0):.1f} img/s", flush=True)
+            if loss is not None:
+                log.scalar("loss", loss, niter)
+                if niter % 10 == 0 and tsp.is_primary():
+                    print(f"iter {niter} loss {loss:.4f} {tsp.meter.recent():.1f} img/s", flush=True)
             if args.max_iters and niter >= args.max_iters:
                 break
         tsp.feed_epoch()
+        log.scalar("learning_rate", cur_lr, niter)
+        log.scalar("images_per_second", tsp.meter.overall(), niter)
         if args.max_iters and niter >= args.max_iters:
             break
-    tsp.stop()
+    for k, loss in enumerate(tsp.stop()):
+        log.scalar("loss", loss, niter + 1 + k)
+    log.save_final(tsp, opt)
+    log.close()
 
 
 if __name__ == "__main__":

@@ -14,7 +14,6 @@ from __future__ import annotations
 import argparse
 import os
 import sys
-import time
 from argparse import Namespace
 
 import torch
@@ -27,6 +26,7 @@ from tspipe_b200.losses import logits_kd, soft_target_kd  # noqa: E402
 from tspipe_b200.models.resnet import resnet_trunk_children, trunk_width  # noqa: E402
 from tspipe_b200.models.vit import vit_classifier  # noqa: E402
 from tspipe_b200.optim import SGD, AdamW  # noqa: E402
+from tspipe_b200.run_log import RunLog  # noqa: E402
 
 
 def create_model(name: str, num_classes: int) -> nn.Sequential:
@@ -76,15 +76,22 @@ def main() -> None:
     lab = torch.randint(0, args.num_class, (args.batch_size,), generator=g)
     if torch.cuda.is_available():
         img, lab = img.pin_memory(), lab.pin_memory()
-    niter, t0 = 0, time.time()
+    log = RunLog(args.artifact_dir, enabled=tsp.is_primary())      # TensorBoard scalars + scalars.csv + model.pth
+    niter = 0
     for epoch in range(args.epochs):
         for _ in range(args.iters_per_epoch):
             loss = tsp.feed(img, img, lab)
             niter += 1
-            if loss is not None and niter % 10 == 0 and tsp.is_primary():
-                print(f"iter {niter} loss {loss:.4f} {niter * args.batch_size / (time.time() - t0):.1f} samples/s", flush=True)
+            if loss is not None:
+                log.scalar("loss", loss, niter)
+                if niter % 10 == 0 and tsp.is_primary():
+                    print(f"iter {niter} loss {loss:.4f} {tsp.meter.recent():.1f} samples/s", flush=True)
         tsp.feed_epoch()
-    tsp.stop()
+        log.scalar("samples_per_second", tsp.meter.overall(), niter)
+    for k, loss in enumerate(tsp.stop()):
+        log.scalar("loss", loss, niter + 1 + k)
+    log.save_final(tsp, opt)
+    log.close()
 
 
 if __name__ == "__main__":

@@ -25,6 +25,19 @@ def _run(cmd, nproc=1, timeout=240):
     return res.stdout
 
 
+def _check_run_artifacts(path, min_losses):
+    """The applications leave TensorBoard-style scalars (always as ``scalars.csv``) and a final ``model.pth`` with the
+    reference's three keys, whose network state dicts cover the whole networks (all partitions joined)."""
+    import torch
+    rows = [l.split(",") for l in (path / "scalars.csv").read_text().splitlines()[1:]]
+    losses = [float(r[3]) for r in rows if r[2] == "loss"]
+    assert len(losses) >= min_losses and all(v == v for v in losses)
+    sd = torch.load(path / "model.pth", weights_only=False)
+    assert set(sd) == {"online_network_state_dict", "target_network_state_dict", "optimizer_state_dict"}
+    assert len(sd["online_network_state_dict"]) > 0 and len(sd["target_network_state_dict"]) > 0
+    assert any(f.name.startswith("events.out.tfevents") for f in path.iterdir())
+
+
 def test_distilbert_app_two_stage_pipeline(tmp_path):
     cfg = _write(tmp_path, "t.yaml", """
 tspipe:
@@ -35,6 +48,7 @@ tspipe:
     out = _run(["benchmarks/distilbert/train.py", "--teacher", "tiny", "--batch-size", "8", "--seq-len", "16",
                 "--iters", "12", "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)], nproc=2)
     assert "iter 10 loss" in out
+    _check_run_artifacts(tmp_path, min_losses=8)
 
 
 def test_soft_target_app_single_stage(tmp_path):
@@ -48,6 +62,7 @@ tspipe:
                 "--image", "32", "--num-class", "10", "--batch-size", "8", "--iters-per-epoch", "11",
                 "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)])
     assert "iter 10 loss" in out
+    _check_run_artifacts(tmp_path, min_losses=8)
 
 
 def test_moco_app_with_replicas(tmp_path):
@@ -61,6 +76,7 @@ tspipe:
                 "--moco-dim", "32", "--moco-mlp-dim", "64", "--max-iters", "11", "--dummy",
                 "--tspipe-config", cfg, "--artifact-dir", str(tmp_path)], nproc=2)
     assert "iter 10 loss" in out
+    _check_run_artifacts(tmp_path, min_losses=8)
 
 
 def test_byol_app_two_stages(tmp_path):
@@ -82,3 +98,4 @@ optimizer: {params: {lr: 0.1, momentum: 0.9, weight_decay: 0.000001}}
     assert "iter 10 loss" in out
     assert (tmp_path / "model_batch5_part0.pt").exists() and (tmp_path / "model_batch10_part1.pt").exists()
     assert (tmp_path / "profile_out.csv").exists()
+    _check_run_artifacts(tmp_path, min_losses=8)

@@ -238,8 +238,11 @@ class StageEngine:
             if self.fused:
                 from ..ops import fused as _fused
                 reserve = rt.get("sm_reserve")
-                if reserve is None:             # stage links: their NCCL kernels must not wait for a persistent kernel
-                    reserve = 8 if topo.pp > 1 else 0
+                if reserve is None:
+                    # library send / receive kernels of the stage links must not queue behind a persistent kernel;
+                    # links over peer memory use copy engines and need no SM
+                    peer_links = bool(rt.get("peer_links", True)) and bool(rt.get("peer_memory", True))
+                    reserve = 8 if (topo.pp > 1 and not peer_links) else 0
                 _fused.set_sm_reserve(int(reserve))
 
         self.online.to(self.device)

@@ -167,6 +167,8 @@ class TSPipe:
         self.last_batch_idx = 0
         self._losses_returned = 0
         self._stopped = False
+        from .run_log import ThroughputMeter
+        self.meter = ThroughputMeter()          # samples per second as seen by feed()
         self._feed_stream = None
         self._resumed_batch = 0         # batch id of the checkpoint this run resumed from (0 = fresh run)
 
@@ -394,6 +396,7 @@ class TSPipe:
         else:
             minis_1, minis_2, minis_t = [view_1], [view_2], [view_target]
         loss = None
+        self.meter.add(bs)
         for v1, v2, vt in zip(minis_1, minis_2, minis_t):
             bid = self.batch_q.get_new_batch_id()
             self.last_batch_idx = bid
