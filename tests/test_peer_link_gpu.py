@@ -131,3 +131,45 @@ def test_two_stage_pipeline_same_losses_over_peer_links_and_library_links():
     b = [x for x in (lib[0] or lib[1])]
     assert len(a) == n_steps and len(b) == n_steps
     torch.testing.assert_close(torch.tensor(a), torch.tensor(b), rtol=1e-6, atol=1e-7)
+
+
+def _split_ssl_rank(rank, world, n_steps):
+    import torch.distributed as dist
+    from tests.test_runtime_cpu import _ssl_batches, _ssl_models
+    from tspipe_b200 import TSPipe
+    from tspipe_b200.comm.peer_link import PeerLink
+    from tspipe_b200.losses import byol_loss, ema_update
+    online, target, predictor = _ssl_models()
+    opt = torch.optim.SGD(list(online.parameters()) + list(predictor.parameters()), lr=0.1, momentum=0.9)
+    cfg = {"model_split": {"online": [8], "target": [5]},
+           "runtime": {"num_ubatch": 2, "bwd_split": 1, "dtype": "fp32", "timeout_s": 120, "placement": "split"},
+           "train": {"deferred_batch_norm": False}}
+    tsp = TSPipe(online, target, predictor, opt, byol_loss, ema_update, 0.9, "", config=cfg, device=f"cuda:{rank}")
+    links = list(tsp.engine.ema_in.values()) + list(tsp.engine.ema_out.values())
+    assert links and all(isinstance(l, PeerLink) for l in links)
+    losses = []
+    for i, (a, b) in enumerate(_ssl_batches(n_steps)):
+        if i == 3:
+            tsp.update_lr(0.05)
+            tsp.update_momentum(0.95)
+        l = tsp.feed(a.pin_memory(), b.pin_memory())
+        if l is not None:
+            losses.append(l)
+    losses += tsp.stop()
+    on, tg = tsp.state_dicts()
+    dist.destroy_process_group()
+    return losses, on, tg
+
+
+def test_split_placement_momentum_teacher_on_two_gpus_matches_oracle():
+    """Teacher on GPU 0, student on GPU 1: the student's parameters reach the teacher over a peer-memory link after
+    every step, the teacher's outputs reach the loss through the peer-mapped ring; same numbers as the CPU oracle."""
+    from tests.test_runtime_cpu import _ssl_oracle
+    n_steps = 7
+    ref_losses, ref_teacher, _ = _ssl_oracle(n_steps, 2, 1)
+    out = run_ranks(_split_ssl_rank, 2, n_steps)
+    torch.testing.assert_close(torch.tensor(out[1][0]), torch.tensor(ref_losses), rtol=2e-3, atol=1e-4)
+    tg = out[0][2]
+    got_t = [v for j in sorted(tg) for k, v in tg[j].items() if "running" not in k and "num_batches" not in k]
+    for a, b in zip(got_t, list(ref_teacher.values())):
+        torch.testing.assert_close(a, b, rtol=2e-3, atol=1e-4)

@@ -299,3 +299,32 @@ def test_async_param_update_emulation_makes_the_student_one_step_stale():
     assert abs(on[0] - on[1]) < 1e-7 and on[2] < on[1]
     assert off[1] < off[0] - 1e-4
     assert abs(on[2] - off[1]) < 1e-6          # version 1 is the same in both runs
+
+
+@pytest.mark.parametrize("split_on,split_tg", [([5, 3], [3, 2]), ([8], [5]), ([3, 5], [1, 4])])
+def test_split_placement_with_momentum_teacher_matches_oracle(split_on, split_tg):
+    """BYOL-style run with the teacher stages on the first ranks and the student stages on the others: the student
+    ranks ship the parameter runs each teacher stage needs after every optimizer step, the teacher folds step k in
+    before its forward of batch k + 2.  Losses, final teacher and final student equal the oracle with the
+    one-step-delayed teacher, for equal and unequal cuts (lr and momentum change on the way)."""
+    n_steps, n_ub = 7, 2
+    cfg = {"model_split": {"online": split_on, "target": split_tg},
+           "runtime": {"num_ubatch": n_ub, "bwd_split": 1, "backend": "gloo", "timeout_s": 60, "placement": "split"},
+           "train": {"deferred_batch_norm": False}}
+    ref_losses, ref_teacher, ref_online = _ssl_oracle(n_steps, n_ub, 1)
+    world = len(split_on) + len(split_tg)
+    out = run_ranks(_ssl_rank, world, cfg, n_steps)
+    losses = out[world - 1][0]                      # the loss rank is the last student rank
+    assert len(losses) == n_steps
+    torch.testing.assert_close(torch.tensor(losses), torch.tensor(ref_losses), rtol=2e-5, atol=1e-6)
+    _, on, tg = out[0]
+    got_t = [v for j in sorted(tg) for k, v in tg[j].items() if "running" not in k and "num_batches" not in k]
+    want_t = list(ref_teacher.values())
+    assert len(got_t) == len(want_t)
+    for a, b in zip(got_t, want_t):
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)
+    got_o = [v for j in sorted(on) for k, v in on[j].items() if "running" not in k and "num_batches" not in k]
+    want_o = [v for k, v in ref_online.items() if "running" not in k and "num_batches" not in k]
+    assert len(got_o) == len(want_o)
+    for a, b in zip(got_o, want_o):
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=1e-6)

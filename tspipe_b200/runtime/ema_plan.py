@@ -50,7 +50,7 @@ def build_ema_plans(partitions_online: Sequence[nn.Module], partitions_target: S
         ps = list(part.parameters())
         for p, off in zip(ps, layout_offsets(ps)):
             student.append((j, off, (p.numel() + ALIGN - 1) // ALIGN * ALIGN, tuple(p.shape)))
-    plans = [EmaPlan() for _ in range(pp)]
+    plans = [EmaPlan() for _ in range(max(pp, len(partitions_target)))]
     i = 0
     for jt, part in enumerate(partitions_target):
         ps = list(part.parameters())
@@ -74,3 +74,22 @@ def build_ema_plans(partitions_online: Sequence[nn.Module], partitions_target: S
                 plans[jt].recv.setdefault(js, []).append((t_off, s_off, n))
                 plans[js].send.setdefault(jt, []).append((s_off, n))
     return plans
+
+
+def split_placement_routes(plans: Sequence[EmaPlan], n_teacher: int, n_student: int
+                           ) -> Tuple[List[Dict[int, List[Tuple[int, int, int]]]], List[Dict[int, List[Tuple[int, int]]]]]:
+    """The same plan for a job whose teacher stages and student stages live on different ranks: nothing is local.
+    Returns ``(sources, dests)``: ``sources[jt][js] = [(t_off, s_off, n)]`` runs teacher stage ``jt`` takes from
+    student stage ``js`` (in the order the student packs them), ``dests[js][jt] = [(s_off, n)]`` runs student stage
+    ``js`` packs for teacher stage ``jt``."""
+    sources: List[Dict[int, List[Tuple[int, int, int]]]] = [dict() for _ in range(n_teacher)]
+    dests: List[Dict[int, List[Tuple[int, int]]]] = [dict() for _ in range(n_student)]
+    for jt in range(n_teacher):
+        plan = plans[jt]
+        if plan.local:
+            sources[jt].setdefault(jt, []).extend(plan.local)
+        for js, runs in plan.recv.items():
+            sources[jt].setdefault(js, []).extend(runs)
+        for js, runs in sources[jt].items():
+            dests[js][jt] = [(s_off, n) for _, s_off, n in runs]
+    return sources, dests

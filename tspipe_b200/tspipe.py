@@ -244,14 +244,22 @@ class TSPipe:
     def _init_split(self, device) -> None:
         """Teacher stages on the first ranks of each replica, student stages on the rest."""
         from .runtime.split_engine import SplitKDEngine, SplitTopology
-        if self.tspipe_mode != TSPipeMode.SUPERVISED_MOMENTUM or self.target_update_fn is not None:
-            raise ValueError("runtime.placement: split supports supervised mode with a frozen teacher")
+        ssl = self.tspipe_mode != TSPipeMode.SUPERVISED_MOMENTUM
+        fn = self.target_update_fn
+        if fn is not None and not getattr(fn, "is_ema", False):
+            raise ValueError("runtime.placement: split updates the teacher with the momentum rule "
+                             "(tspipe_b200.losses.ema_update) or not at all")
+        if ssl and fn is None:
+            warnings.warn("self-supervised split placement without a target update function: frozen teacher")
+        if fn is not None and self.config["runtime"].get("resume"):
+            raise ValueError("resuming a momentum teacher in split placement is not supported")
         split = self.config["model_split"]
         if split["online"] is None or split["target"] is None:
             raise BalanceError("split placement needs model_split.online and model_split.target")
         pt_, ps = len(split["target"]), len(split["online"])
         dp = self.config["runtime"]["dp_replicas"] or self.world // (pt_ + ps)
-        self.topo = SplitTopology(pt_, ps, dp, device, timeout_s=self.config["runtime"]["timeout_s"])
+        self.topo = SplitTopology(pt_, ps, dp, device, timeout_s=self.config["runtime"]["timeout_s"],
+                                  ema_pairs=fn is not None)
         if self.config["runtime"]["num_ubatch"] is None:
             self.config["runtime"]["num_ubatch"] = max(ps - 1, 1)
         self.config["train"]["deferred_batch_norm"] = False
@@ -259,6 +267,10 @@ class TSPipe:
         self.partitions_online, self.partitions_target = split_module(
             self.module_online, self.module_target, self.module_predictor, split["online"], split["target"])
         self.ema_plans = None
+        routes = None
+        if fn is not None:
+            from .runtime.ema_plan import build_ema_plans, split_placement_routes
+            routes = split_placement_routes(build_ema_plans(self.partitions_online, self.partitions_target), pt_, ps)
         t = self.topo
         part = self.partitions_target[t.stage] if t.is_teacher else self.partitions_online[t.stage]
         opt = None
@@ -266,7 +278,8 @@ class TSPipe:
             rebind_optimizer(self.optimizer, list(part.parameters()))
             opt = self.optimizer
         self.engine = SplitKDEngine(t, self.config, part, opt, self.loss_fn, self.target_train_mode,
-                                    self.scatter_gather_fn, self.args, self.extra_args)
+                                    self.scatter_gather_fn, self.args, self.extra_args, ssl=ssl,
+                                    momentum=self.momentum, ema_routes=routes)
         self._maybe_resume()
         self.engine.on_batch_done = self._on_batch_done
         self._done_batches = 0
