@@ -206,7 +206,7 @@ def case_infonce():
     import torch.nn.functional as F
     from tspipe_b200.ops import fused, gemm
     dev = torch.device("cuda")
-    n, d, temp = 4096, 256, 0.2
+    n, d, temp = (int(sys.argv[2]) if len(sys.argv) > 2 else 4096), 256, 0.2
     q = torch.randn(n, d, device=dev, requires_grad=True)
     k = torch.randn(n, d, device=dev)
 
@@ -219,15 +219,31 @@ def case_infonce():
         logits = F.normalize(q, dim=1) @ F.normalize(k, dim=1).t() / temp
         (F.cross_entropy(logits, torch.arange(n, device=dev)) * 2 * temp).backward()
 
-    t = _time(ours, n=10)
+    def device_time(fn):
+        """Device time of one call with the launch overhead taken out: the call is captured into a CUDA graph and
+        the replays are timed (a dozen small launches per call would otherwise be bound by the host)."""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return _time(g.replay, n=10)
+
+    t = device_time(ours)
+    gemm.set_nce_key_split(False)
+    t1 = device_time(ours)
+    gemm.set_nce_key_split(True)
     gemm.set_fused_nce(False)
-    tu = _time(ours, n=10)
+    tu = device_time(ours)
     gemm.set_fused_nce(True)
-    tr = _time(ref, n=10)
+    tr = device_time(ref)
     gemm.check_status()
     flops = 2 * 2 * n * n * d          # scores + weighted sum of keys
-    print(f"info_nce fwd+bwd [{n},{d}]: fused attention-style kernel {t:7.1f} us ({flops / t / 1e6:6.1f} TFLOP/s incl. "
-          f"normalisation kernels) | logits GEMM + CE kernel {tu:7.1f} us | library ops {tr:7.1f} us")
+    print(f"info_nce fwd+bwd [{n},{d}] (graph replays, device time): fused kernel with the keys split over "
+          f"{gemm.nce_key_chunks(n, n)} chunks {t:7.1f} us ({flops / t / 1e6:6.1f} TFLOP/s incl. normalisation and merge "
+          f"kernels) | one CTA per query tile {t1:7.1f} us | logits GEMM + CE kernel {tu:7.1f} us | library ops "
+          f"{tr:7.1f} us")
 
 
 def case_attn():

@@ -326,6 +326,30 @@ int tsp_ipc_import(const unsigned char* handle64, void** base) {
 
 int tsp_ipc_close(void* base) { return (int)cudaIpcCloseMemHandle(base); }
 
+// Capability query only: 1 when `device` can take part in NVLink multicast objects (the in-switch reduction path that
+// `multimem` instructions address), 0 when it cannot, negative when the driver cannot be asked.  Nothing is created or
+// bound here: a rank that dies while its memory is bound to a multicast object disturbs the other GPUs, so the
+// kernels of this library move data with plain peer loads / stores and copy engines and only report the capability.
+int tsp_multicast_supported(int device) {
+  typedef int (*GetAttrFn)(int*, int, int);
+  static GetAttrFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuDeviceGetAttribute", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess && p != nullptr) {
+      fn = (GetAttrFn)p;
+    } else {
+      (void)cudaGetLastError();
+      return -1;
+    }
+  }
+  int value = 0;
+  const int kMulticastSupported = 132;          // CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED
+  if (fn(&value, kMulticastSupported, device) != 0) return -2;
+  return value ? 1 : 0;
+}
+
 // Stream-ordered copy between any two device addresses this process can reach (own memory or a mapped peer
 // buffer).  The driver moves the bytes with a copy engine over NVLink: no SM is involved, so a transfer never
 // competes with the persistent compute kernels for a place on the GPU.

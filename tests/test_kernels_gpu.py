@@ -221,14 +221,21 @@ def test_fused_batchnorm_act(dtype, shape, residual, relu):
     yr = F.batch_norm(xr, None, None, wr, br, training=True, eps=bn.eps)
     if residual:
         yr = yr + rr
+    # bf16: an element whose pre-activation is within rounding distance of zero may land on the other side of the
+    # ReLU than in the fp32 reference, which flips its whole gradient; such elements are left out of the
+    # element-wise comparison (their effect on the channel sums stays far below the tolerance)
+    keep = torch.ones_like(yr, dtype=torch.bool)
     if relu:
+        if dtype == torch.bfloat16:
+            keep = yr.detach().abs() > 0.05
         yr = F.relu(yr)
     yr.backward(g.float())
     tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
-    torch.testing.assert_close(y.float(), yr.detach(), **tol)
-    torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
+    assert keep.float().mean() > 0.9
+    torch.testing.assert_close(y.float()[keep], yr.detach()[keep], **tol)
+    torch.testing.assert_close(x.grad.float()[keep], xr.grad[keep], **tol)
     if residual:
-        torch.testing.assert_close(res.grad.float(), rr.grad, **tol)
+        torch.testing.assert_close(res.grad.float()[keep], rr.grad[keep], **tol)
     wtol = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=5e-2, atol=0.5)
     torch.testing.assert_close(bn.weight.grad, wr.grad, **wtol)
     torch.testing.assert_close(bn.bias.grad, br.grad, **wtol)
@@ -446,3 +453,13 @@ def test_mlm_head_vocab_padding_keeps_loss_and_gradients():
     ref.backward()
     torch.testing.assert_close(loss, ref, rtol=1e-3, atol=1e-3)
     torch.testing.assert_close(x_s.grad, xr.grad, rtol=1e-2, atol=1e-4)
+
+
+def test_multicast_capability_query_answers():
+    """The NVLS capability probe is a driver attribute query: it answers True or False on a CUDA box and creates
+    nothing."""
+    from tspipe_b200.comm import peer
+    before = torch.cuda.memory_allocated()
+    ans = peer.multicast_supported(0)
+    assert ans in (True, False)
+    assert torch.cuda.memory_allocated() == before

@@ -130,3 +130,16 @@ def pointer_table(buffers: Sequence[Union[torch.Tensor, PeerView]]):
     for i, t in enumerate(buffers):
         arr[i] = t.data_ptr()
     return arr
+
+
+def multicast_supported(device: Optional[int] = None) -> Optional[bool]:
+    """Whether the GPU can join NVLink multicast objects (NVLS, what ``multimem`` instructions address): a capability
+    query through the driver, nothing is allocated or bound.  ``None`` when it cannot be asked (no CUDA, old driver).
+    The runtime records the answer at start-up; its cross-GPU kernels use peer loads / stores either way."""
+    if not torch.cuda.is_available():
+        return None
+    from ..ops import fused
+    L = fused.lib()
+    L.tsp_multicast_supported.restype = ctypes.c_int
+    code = int(L.tsp_multicast_supported(ctypes.c_int(torch.cuda.current_device() if device is None else device)))
+    return None if code < 0 else bool(code)

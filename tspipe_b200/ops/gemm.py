@@ -308,6 +308,28 @@ def set_fused_nce(on: bool) -> None:
     _fused_nce = bool(on)
 
 
+_NCE_KEY_SPLIT = True
+
+
+def set_nce_key_split(flag: bool) -> None:
+    """Split the keys of the fused contrastive loss over the grid (default) or run one CTA per query tile."""
+    global _NCE_KEY_SPLIT
+    _NCE_KEY_SPLIT = bool(flag)
+
+
+def nce_key_chunks(n_queries: int, n_keys: int, target_ctas: int = 120) -> int:
+    """Into how many chunks the fused contrastive loss splits the keys so that (query tiles) x (chunks) fills the
+    GPU: the smallest power of two that reaches ``target_ctas`` CTAs, as long as every chunk keeps at least two
+    64-row key tiles and the keys divide evenly."""
+    if not _NCE_KEY_SPLIT:
+        return 1
+    tiles = -(-n_queries // 128)
+    c = 1
+    while tiles * c < target_ctas and n_keys % (2 * c * 64) == 0 and n_keys // (2 * c) >= 128:
+        c *= 2
+    return c
+
+
 class _FusedNCE(torch.autograd.Function):
     """``2T * mean_i(logsumexp_j(q_i.k_j / T) - q_i.k_i / T)`` for unit-norm rows, forward and backward from ONE
     pass of the fused attention kernel with V = K: ``lse`` gives the loss, ``O_i = sum_j p_ij k_j`` the gradient
@@ -317,13 +339,30 @@ class _FusedNCE(torch.autograd.Function):
     def forward(ctx, qn, kn16, temp):
         from .attention import flash_fwd
         n, d = qn.shape
+        nk = kn16.shape[0]
         q16 = qn.to(torch.bfloat16)
-        o, lse = flash_fwd(q16.view(1, 1, n, d), kn16.view(1, 1, -1, d), kn16.view(1, 1, -1, d), scale=1.0 / temp,
-                           fixed_max=1.0 / temp, out_dtype=torch.float32, want_lse=True)
+        c = nce_key_chunks(n, nk)
+        if c == 1:
+            o, lse = flash_fwd(q16.view(1, 1, n, d), kn16.view(1, 1, -1, d), kn16.view(1, 1, -1, d), scale=1.0 / temp,
+                               fixed_max=1.0 / temp, out_dtype=torch.float32, want_lse=True)
+            o, lse = o.reshape(n, d), lse.view(n)
+        else:
+            # Keys split over the grid: chunk c of the keys is "head" c of the kernel's (query tile, head) grid, every
+            # head sees the same queries.  Each CTA returns its chunk's softmax-weighted key sum and log-sum-exp
+            # (exact: the scores are bounded by 1/T, so all chunks use the same fixed maximum); the chunks are then
+            # merged with their softmax weights.
+            q_rep = q16.unsqueeze(0).expand(c, n, d).contiguous().view(1, c, n, d)
+            k_chunks = kn16.view(1, c, nk // c, d)
+            o_part, lse_part = flash_fwd(q_rep, k_chunks, k_chunks, scale=1.0 / temp, fixed_max=1.0 / temp,
+                                         out_dtype=torch.float32, want_lse=True)
+            lse_part = lse_part.view(c, n)
+            lse = torch.logsumexp(lse_part, dim=0)
+            w = torch.exp(lse_part - lse)                                   # [c, n], sums to 1 over the chunks
+            o = torch.einsum("cn,cnd->nd", w, o_part[0])
         pos = (q16.float() * kn16[:n].float()).sum(1) / temp
-        ctx.save_for_backward(o.reshape(n, d), kn16)
+        ctx.save_for_backward(o, kn16)
         ctx.n, ctx.qdtype = n, qn.dtype
-        return (lse.view(n) - pos).mean() * (2 * temp)
+        return (lse - pos).mean() * (2 * temp)
 
     @staticmethod
     def backward(ctx, g):

@@ -239,10 +239,12 @@ class StageEngine:
                 from ..ops import fused as _fused
                 reserve = rt.get("sm_reserve")
                 if reserve is None:
-                    # library send / receive kernels of the stage links must not queue behind a persistent kernel;
-                    # links over peer memory use copy engines and need no SM
+                    # kernels of the stage links must not queue behind a persistent kernel that fills every SM:
+                    # the library's send / receive kernels, or the one-thread ordering kernels of the peer-memory
+                    # links (their bytes move by copy engine, but a signal that waits for a whole convolution to
+                    # finish adds its latency to every hop of the pipeline)
                     peer_links = bool(rt.get("peer_links", True)) and bool(rt.get("peer_memory", True))
-                    reserve = 8 if (topo.pp > 1 and not peer_links) else 0
+                    reserve = (4 if peer_links else 8) if topo.pp > 1 else 0
                 _fused.set_sm_reserve(int(reserve))
 
         self.online.to(self.device)
@@ -358,6 +360,9 @@ class StageEngine:
                 and hasattr(opt, "enable_dp") and type(opt).__name__ in ("LARS", "AdamW")):
             return
         from ..comm import peer
+        self.nvls_capable = peer.multicast_supported(self.device.index)
+        if topo.rank == 0:
+            Log.i(f"NVLink multicast (NVLS) capability: {self.nvls_capable}; gradients move by peer loads / stores")
         grads = peer.exchange(self.flat_online.grad, topo.dp_group, topo.dp_ranks)
         params = peer.exchange(self.flat_online.data, topo.dp_group, topo.dp_ranks)
         opt.enable_dp(topo.dp_group, grads, params, topo.replica)
