@@ -227,7 +227,9 @@ def run_substitute(a) -> None:
     metric = {"moco": "MoCo-v3 ViT-B/16 training throughput", "distilbert": "DistilBERT-style KD training throughput",
               "kd": "Soft-target KD ViT-L/16 -> ViT-B/16 training throughput"}[w]
     unit = "images/s" if w == "moco" else "samples/s"
-    want = getattr(a, "ref_dtype", "both")
+    want = getattr(a, "ref_dtype", "auto")
+    if want == "auto":
+        want = "both"
     try:
         main = run("fp32" if want == "fp32" else "bf16")
         extra = run("fp32") if want == "both" else None

@@ -73,7 +73,7 @@ def parse(argv=None):
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"], help="compute dtype (fp32 = TF32 tensor cores)")
     p.add_argument("--host-dtype", default="bf16", choices=["bf16", "fp32"],
                    help="dtype of the pinned host inputs of the end-to-end pass (image workloads)")
-    p.add_argument("--ref-dtype", default="both", choices=["fp32", "bf16", "both"],
+    p.add_argument("--ref-dtype", default="auto", choices=["auto", "fp32", "bf16", "both"],
                    help="reference arm: as shipped (fp32), under bf16 autocast, or both")
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
