@@ -1,4 +1,5 @@
-// 3x3 / stride 2 / pad 1 max pooling for channels-last activations, forward and backward (sm_100a).
+// 3x3 / stride 2 / pad 1 max pooling and global average pooling for channels-last activations, forward and backward
+// (sm_100a).
 //
 // ResNet stem (`benchmarks/byol/models/resnet_base_network.py` via torchvision's `maxpool`).  The library's NHWC
 // kernels take ~0.4 ms forward / ~0.9 ms backward on a [128, 64, 112, 112] bf16 activation; both are pure
@@ -93,6 +94,50 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ 
   }
 }
 
+// Global average pool of a channels-last activation: y[b, c] = mean over the hw positions of x[b, :, c].  One thread
+// per (image, 8 channels): consecutive threads read consecutive 16-byte groups of a pixel's channel vector.
+template <typename T>
+__global__ void __launch_bounds__(256) avgpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int n, int hw,
+                                                          int c) {
+  const int cpv = c >> 3;
+  const int64_t total = (int64_t)n * cpv;
+  const float inv = 1.f / (float)hw;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cpv);
+    const int64_t b = i / cpv;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int p = 0; p < hw; ++p) {
+      float v[8];
+      tsp::ld8(x, (b * hw + p) * c + cg * 8, v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= inv;
+    tsp::st8(y, b * c + cg * 8, acc);
+  }
+}
+
+// dx[b, p, c] = dy[b, c] / hw
+template <typename T>
+__global__ void __launch_bounds__(256) avgpool_bwd_kernel(const T* __restrict__ dy, T* __restrict__ dx, int n, int hw,
+                                                          int c) {
+  const int cpv = c >> 3;
+  const int64_t total = (int64_t)n * hw * cpv;
+  const float inv = 1.f / (float)hw;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int cg = (int)(i % cpv);
+    const int64_t b = i / cpv / hw;
+    float v[8];
+    tsp::ld8(dy, b * c + cg * 8, v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] *= inv;
+    tsp::st8(dx, i * 8, v);
+  }
+}
+
 inline int blocks_for(int64_t n) {
   int64_t b = (n + 255) / 256;
   if (b > 148 * 16) b = 148 * 16;
@@ -129,6 +174,29 @@ int tsp_maxpool3x3s2_bwd(const void* dy, const uint8_t* idx, void* dx, int n, in
                                                                 w, c, ho, wo);
   else
     maxpool_bwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)dy, idx, (float*)dx, n, h, w, c, ho, wo);
+  return TSP_LAUNCH_CHECK();
+}
+
+// x [n, h*w, c] channels-last -> y [n, c] (mean over the positions); c a multiple of 8.
+int tsp_avgpool_fwd(const void* x, void* y, int n, int hw, int c, int dtype, cudaStream_t stream) {
+  if (n <= 0 || hw <= 0) return 0;
+  if (c % 8 != 0) return -3;
+  const int grid = blocks_for((int64_t)n * (c / 8));
+  if (dtype == TSP_DTYPE_BF16)
+    avgpool_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, n, hw, c);
+  else
+    avgpool_fwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (float*)y, n, hw, c);
+  return TSP_LAUNCH_CHECK();
+}
+
+int tsp_avgpool_bwd(const void* dy, void* dx, int n, int hw, int c, int dtype, cudaStream_t stream) {
+  if (n <= 0 || hw <= 0) return 0;
+  if (c % 8 != 0) return -3;
+  const int grid = blocks_for((int64_t)n * hw * (c / 8));
+  if (dtype == TSP_DTYPE_BF16)
+    avgpool_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, n, hw, c);
+  else
+    avgpool_bwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)dy, (float*)dx, n, hw, c);
   return TSP_LAUNCH_CHECK();
 }
 

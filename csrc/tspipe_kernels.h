@@ -77,6 +77,8 @@ int tsp_maxpool3x3s2_fwd(const void* x, void* y, uint8_t* idx, int n, int h, int
                          cudaStream_t stream);
 int tsp_maxpool3x3s2_bwd(const void* dy, const uint8_t* idx, void* dx, int n, int h, int w, int c, int dtype,
                          cudaStream_t stream);
+int tsp_avgpool_fwd(const void* x, void* y, int n, int hw, int c, int dtype, cudaStream_t stream);
+int tsp_avgpool_bwd(const void* dy, void* dx, int n, int hw, int c, int dtype, cudaStream_t stream);
 
 // ---- gemm_tcgen05.cu ------------------------------------------------------------------------------------------
 int tsp_gemm_bf16_tn(const void* a, const void* b, void* c, const float* bias, int m, int n, int k, int lda, int ldb,

@@ -463,3 +463,26 @@ def test_multicast_capability_query_answers():
     ans = peer.multicast_supported(0)
     assert ans in (True, False)
     assert torch.cuda.memory_allocated() == before
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(8, 64, 7, 7), (3, 2048, 7, 7), (4, 24, 5, 3), (2, 512, 14, 14)])
+def test_global_average_pool_matches_library(dtype, shape):
+    """Channels-last global average pooling, forward and backward, against fp32 ``adaptive_avg_pool2d``."""
+    from tspipe_b200.ops.pool import GlobalAvgPool, _GlobalAvgPool
+    torch.manual_seed(5)
+    x = torch.randn(shape, device=_dev()).to(dtype).contiguous(memory_format=torch.channels_last).requires_grad_()
+    g = torch.randn(shape[0], shape[1], 1, 1, device=_dev()).to(dtype)
+    from tspipe_b200.ops import fused
+    before = fused.LAUNCHES
+    y = GlobalAvgPool()(x)
+    y.backward(g)
+    assert fused.LAUNCHES == before + 2                    # the kernels ran, not the fallback
+    xr = x.detach().float().requires_grad_()
+    yr = F.adaptive_avg_pool2d(xr, 1)
+    yr.backward(g.float())
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    assert y.shape == yr.shape
+    torch.testing.assert_close(y.float(), yr.detach(), **tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, **tol)
+    assert x.grad.is_contiguous(memory_format=torch.channels_last)

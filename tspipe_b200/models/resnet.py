@@ -15,7 +15,7 @@ import torch
 from torch import nn
 
 from ..ops.conv import conv_bn_act
-from ..ops.pool import MaxPool3x3s2
+from ..ops.pool import GlobalAvgPool, MaxPool3x3s2
 
 
 def _downsample(down: nn.Module, x: torch.Tensor) -> torch.Tensor:
@@ -91,7 +91,7 @@ def resnet_trunk_children(name: str = "resnet50") -> "OrderedDict[str, nn.Module
                                      nn.BatchNorm2d(planes * block.expansion))
             ch[f"layer{li + 1}_{bi}"] = block(inplanes, planes, stride, down)
             inplanes = planes * block.expansion
-    ch["avgpool"] = nn.AdaptiveAvgPool2d(1)
+    ch["avgpool"] = GlobalAvgPool()
     ch["reshape"] = Reshape2d()
     for m in ch.values():
         for mod in m.modules():

@@ -1,4 +1,5 @@
-"""Channels-last 3x3 / stride-2 / pad-1 max pooling (``csrc/pool.cu``) with a library fallback."""
+"""Channels-last 3x3 / stride-2 / pad-1 max pooling and global average pooling (``csrc/pool.cu``) with library
+fallbacks."""
 from __future__ import annotations
 
 import ctypes as _c
@@ -57,3 +58,47 @@ class MaxPool3x3s2(nn.MaxPool2d):
                 and x.stride() == (x.shape[2] * x.shape[3] * x.shape[1], 1, x.shape[3] * x.shape[1], x.shape[1])):
             return _MaxPool.apply(x)
         return F.max_pool2d(x, 3, 2, 1)
+
+
+class _GlobalAvgPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        n, c, h, w = x.shape
+        y = torch.empty((n, c, 1, 1), dtype=x.dtype, device=x.device)
+        L = _f.lib()
+        L.tsp_avgpool_fwd.restype = _c.c_int
+        with _f.on_device(x.device):
+            _f._check(L.tsp_avgpool_fwd(_f._ptr(x), _f._ptr(y), _c.c_int(n), _c.c_int(h * w), _c.c_int(c),
+                                        _c.c_int(_f._dt(x)), _f._stream()), "tsp_avgpool_fwd")
+        _f._count()
+        ctx.shape = (n, c, h, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, c, h, w = ctx.shape
+        dy = dy.reshape(n, c).contiguous()
+        dx = torch.empty((n, c, h, w), dtype=dy.dtype, device=dy.device, memory_format=torch.channels_last)
+        L = _f.lib()
+        L.tsp_avgpool_bwd.restype = _c.c_int
+        with _f.on_device(dy.device):
+            _f._check(L.tsp_avgpool_bwd(_f._ptr(dy), _f._ptr(dx), _c.c_int(n), _c.c_int(h * w), _c.c_int(c),
+                                        _c.c_int(_f._dt(dy)), _f._stream()), "tsp_avgpool_bwd")
+        _f._count()
+        return dx
+
+
+class GlobalAvgPool(nn.AdaptiveAvgPool2d):
+    """``nn.AdaptiveAvgPool2d(1)`` that uses the channels-last kernel when it applies (the pooling in front of the
+    ResNet heads, `benchmarks/byol/models/resnet_base_network.py` via torchvision's ``avgpool`` in the reference)."""
+
+    def __init__(self):
+        super().__init__(1)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
+        from . import bn as _bn
+        if (x.is_cuda and _bn._ENABLED and x.dim() == 4 and x.shape[1] % 8 == 0
+                and x.dtype in (torch.float32, torch.bfloat16) and x.shape[2] * x.shape[3] > 1
+                and x.stride() == (x.shape[2] * x.shape[3] * x.shape[1], 1, x.shape[3] * x.shape[1], x.shape[1])):
+            return _GlobalAvgPool.apply(x)
+        return F.adaptive_avg_pool2d(x, 1)
