@@ -123,9 +123,12 @@ class StudentStageGraphs:
         if slot.fwd is None:
             try:
                 self._capture(slot, leaves, tpos, tree, wrapped, segs)
-            except Exception:
+            except Exception as e:  # noqa: BLE001 - a stage that cannot be recorded keeps running eagerly
                 slot.failed = True
-                raise
+                slot.fwd = slot.bwd = None
+                from ..logger import Log
+                Log.w(f"stage not captured into CUDA graphs ({type(e).__name__}: {e}); it stays on the eager path")
+                return None, None
         with torch.no_grad():
             for i in tpos:
                 slot.static_in[i].copy_(leaves[i])
