@@ -85,8 +85,8 @@ class PeerLink:
         self.channels_last = bool(channels_last)
         # links of the same name made one after the other in a process (several pipelines over one process group)
         # get store keys of their own; both ends create their links in the same order
-        n = PeerLink._instances.get((id(store), name), 0)
-        PeerLink._instances[(id(store), name)] = n + 1
+        n = PeerLink._instances.get(name, 0)
+        PeerLink._instances[name] = n + 1
         self.store, self.name, self.device = store, f"{name}#{n}", device
         self.slots, self.limit_ms = max(int(slots), 1), int(limit_ms)
         self.cuda = True
@@ -101,7 +101,6 @@ class PeerLink:
         self._ring: Optional[torch.Tensor] = None      # receiver: current ring
         self._old_rings: List[torch.Tensor] = []
         self._ring_ptr = 0            # sender: mapped base of the receiver's ring
-        self._keep: List[Any] = []
         L = fused.lib()
         for fn in ("tsp_signal_arrive", "tsp_signal_wait", "tsp_copy_async"):
             getattr(L, fn).restype = _c.c_int

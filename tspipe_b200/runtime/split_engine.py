@@ -61,6 +61,7 @@ class PeerMatrix(PeerView):
 
 class SplitTopology:
     """Per-replica layout ``[teacher stages | student stages]`` and its process groups."""
+    _instances = 0
 
     def __init__(self, pt_: int, ps: int, dp: int, device: torch.device, timeout_s: float = 600.0,
                  ema_pairs: bool = False):
@@ -107,7 +108,8 @@ class SplitTopology:
                 if self.rank in ranks:
                     self.dp_group = g
         from torch.distributed.distributed_c10d import _get_default_store
-        self.store = dist.PrefixStore("tspipe_ctl", _get_default_store())
+        SplitTopology._instances += 1       # every pipeline of a job gets its own key space in the store
+        self.store = dist.PrefixStore(f"tspipe_split_ctl{SplitTopology._instances}", _get_default_store())
 
     @property
     def is_cuda(self) -> bool:
