@@ -148,7 +148,10 @@ class MetaBoard:
     def fetch(self, link: str, net: str, batch: int) -> Any:
         key = self._key(link, net, batch)
         if key not in self._got:
-            self._got[key] = pickle.loads(self.store.get(key))
+            import warnings
+            with warnings.catch_warnings():             # tree specs of older pickles warn about their own class names
+                warnings.simplefilter("ignore", FutureWarning)
+                self._got[key] = pickle.loads(self.store.get(key))
             try:
                 self.store.delete_key(key)
             except Exception:
