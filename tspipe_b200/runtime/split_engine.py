@@ -158,15 +158,46 @@ class SplitKDEngine:
         self.compute = torch.cuda.Stream(self.device) if self.cuda else None
         base = topo.replica * topo.pp + (0 if topo.is_teacher else topo.pt)
         me = topo.rank
+        from ..comm.peer_link import make_link
+        peer_links = self.cuda and bool(rt.get("peer_links", True)) and bool(rt.get("peer_memory", True))
+        if self.fused:
+            # the one-thread ordering kernels of the peer-memory links (or the library's send / receive kernels) must
+            # not queue behind a persistent GEMM that fills every SM
+            from ..ops import fused as _fused
+            reserve = rt.get("sm_reserve")
+            _fused.set_sm_reserve(int(reserve) if reserve is not None else (4 if peer_links else 8))
+
+        def link(group, peer_rank: int, tag: str):
+            # peer memory + copy engines between GPUs of this node, the torch.distributed link otherwise; the name is
+            # the same on both ends (boundaries are numbered by their lower rank)
+            peer_dev = (self.device.index + peer_rank - me) if self.cuda else None
+            if peer_dev is not None and not 0 <= peer_dev < torch.cuda.device_count():
+                peer_dev = None
+            return make_link(group, peer_rank, self.device, store=topo.store, name=f"plink/split/{tag}",
+                             peer_device=peer_dev, use_peer=peer_links,
+                             limit_ms=int(min(max(float(rt["timeout_s"]), 1.0), 600.0) * 1000))
+
+        # stage boundaries inside the two chains: torch.distributed links
         self.fwd_in = Link(topo.fwd[me - 1], me - 1, self.device) if not topo.is_first else None
         self.fwd_out = Link(topo.fwd[me], me + 1, self.device) if not topo.is_last else None
         self.bwd_in = Link(topo.bwd[me], me + 1, self.device) if (not topo.is_teacher and not topo.is_last) else None
         self.bwd_out = Link(topo.bwd[me - 1], me - 1, self.device) if (not topo.is_teacher and not topo.is_first) else None
         other = None
+        self.fill_link = self.free_link = None
         if topo.is_teacher_out_rank or topo.is_loss_rank:
             other = topo.pair[1] if topo.is_teacher_out_rank else topo.pair[0]
-            self.fill_link = Link(topo.tok_fill, other, self.device)
-            self.free_link = Link(topo.tok_free, other, self.device)
+            # "slot filled" / "slot free" tokens.  A library receive for a token stays resident on the GPU until the
+            # token comes (a whole batch later), in the way of every persistent GEMM launched meanwhile, so with a
+            # frozen teacher the tokens go over peer-memory links.  With a momentum teacher they stay on the library:
+            # a peer link's first send waits on the host for the receiver's first post, the teacher posts its first
+            # "free" receive only at batch 3, which needs the student's parameters of step 1, which the student
+            # sends only after that first "free" send has returned.
+            if ema_routes is None:
+                self.fill_link = link(topo.tok_fill, other, f"fill{topo.pair[0]}")
+                self.free_link = link(topo.tok_free, other, f"free{topo.pair[0]}")
+            else:
+                self.fill_link = Link(topo.tok_fill, other, self.device)
+                self.free_link = Link(topo.tok_free, other, self.device)
         self.meta = MetaBoard(topo.store, topo.replica)
         self.ring: Optional[List[torch.Tensor]] = None
         self.ring_views: Optional[List[Any]] = None
@@ -214,10 +245,14 @@ class SplitKDEngine:
         links = sorted(set(list(t.fwd.items()) + [(k + 10 ** 6, v) for k, v in t.bwd.items()]), key=lambda kv: kv[0])
         for key, g in links:
             lo = key % 10 ** 6
-            src, dst = (lo, lo + 1) if key < 10 ** 6 else (lo + 1, lo)
+            down = key < 10 ** 6
+            src, dst = (lo, lo + 1) if down else (lo + 1, lo)
+            mine = ((self.fwd_out if down else self.bwd_in) if t.rank == lo else (self.fwd_in if down else self.bwd_out))
+            if not isinstance(mine, Link):
+                continue                                # a peer-memory link (or none): no communicator behind it
             x = torch.zeros(1, device=self.device)
             (dist.send(x, dst, group=g) if t.rank == src else dist.recv(x, src, group=g))
-        if t.tok_fill is not None:
+        if t.tok_fill is not None and isinstance(self.fill_link, Link):
             a, b = t.pair
             x = torch.zeros(1, device=self.device)
             (dist.send(x, b, group=t.tok_fill) if t.rank == a else dist.recv(x, a, group=t.tok_fill))
@@ -539,7 +574,7 @@ class SplitKDEngine:
         if self.topo.is_teacher and self.ema_sources is not None:
             with self._on_compute():
                 self._apply_teacher_updates(done)       # the student's last two steps are still on their way
-        for link in [self.fwd_out, self.bwd_out] + list(self.ema_out.values()):
+        for link in [self.fwd_out, self.bwd_out, self.fill_link, self.free_link] + list(self.ema_out.values()):
             if link is not None:
                 link.flush()
         if self.cuda:
