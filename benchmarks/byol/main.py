@@ -25,6 +25,7 @@ from tspipe_b200.dataloader import DummyInputGenerator, FastDataLoader  # noqa: 
 from tspipe_b200.losses import byol_loss, ema_update  # noqa: E402
 from tspipe_b200.models.resnet import byol_networks  # noqa: E402
 from tspipe_b200.optim import LARS, SGD, AdamW  # noqa: E402
+from tspipe_b200.plain_trainer import PlainTrainer  # noqa: E402
 from tspipe_b200.profiler import TSPipeProfiler  # noqa: E402
 from tspipe_b200.run_log import RunLog  # noqa: E402
 from tspipe_b200.schedules import cosine_lr, cosine_momentum  # noqa: E402
@@ -35,6 +36,8 @@ def main() -> None:
     ap.add_argument("--config", default=os.path.join(os.path.dirname(__file__), "config.yaml"))
     ap.add_argument("--artifact-dir", default="runs/byol")
     ap.add_argument("--max-iters", type=int, default=0)
+    ap.add_argument("--plain", action="store_true",
+                    help="the reference's non-pipelined trainer (one device, immediate teacher) for loss-curve comparison")
     args, _ = ap.parse_known_args()
     cfg = yaml.safe_load(open(args.config))
     head = cfg["network"]["projection_head"]
@@ -50,7 +53,11 @@ def main() -> None:
     optimizer = opt_cls(params, **opt_args)
     m0, epochs = cfg["trainer"]["m"], cfg["trainer"]["max_epochs"]
     with TSPipeProfiler(filename=os.path.join(args.artifact_dir, "profile_out.csv")) as prof:
-        tsp = TSPipe(online, target, predictor, optimizer, byol_loss, ema_update, m0, args.artifact_dir, profiler=prof)
+        if args.plain:
+            tsp = PlainTrainer(online, target, predictor, optimizer, byol_loss, ema_update, m0, args.artifact_dir)
+        else:
+            tsp = TSPipe(online, target, predictor, optimizer, byol_loss, ema_update, m0, args.artifact_dir,
+                         profiler=prof)
         if cfg["trainer"]["dummy_input"]:
             image = ast.literal_eval(cfg["data_transforms"]["input_shape"])[0]
             loader = DummyInputGenerator(bs, input_shape=image, pin=torch.cuda.is_available())

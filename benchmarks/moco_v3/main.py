@@ -28,6 +28,7 @@ from tspipe_b200.dataloader import DummyInputGenerator, FastDataLoader  # noqa: 
 from tspipe_b200.losses import ema_update, moco_loss  # noqa: E402
 from tspipe_b200.models.vit import moco_vit_networks  # noqa: E402
 from tspipe_b200.optim import LARS, AdamW  # noqa: E402
+from tspipe_b200.plain_trainer import PlainTrainer  # noqa: E402
 from tspipe_b200.run_log import RunLog  # noqa: E402
 
 
@@ -51,6 +52,8 @@ def main() -> None:
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--max-iters", type=int, default=0)
     ap.add_argument("--artifact-dir", default="runs/moco_v3")
+    ap.add_argument("--plain", action="store_true",
+                    help="the reference's non-pipelined trainer (one device, immediate momentum encoder)")
     args, _ = ap.parse_known_args()
 
     base, momentum, predictor = moco_vit_networks(args.arch, args.moco_dim, args.moco_mlp_dim, args.stop_grad_conv1)
@@ -58,8 +61,12 @@ def main() -> None:
     lr = args.lr * args.batch_size / 256
     opt = AdamW(params, lr=lr, weight_decay=args.weight_decay) if args.optimizer == "adamw" else \
         LARS(params, lr=lr, weight_decay=args.weight_decay, momentum=0.9)
-    tsp = TSPipe(base, momentum, predictor, opt, moco_loss, ema_update, args.moco_m, args.artifact_dir,
-                 extra_args=Namespace(moco_t=args.moco_t))
+    if args.plain:
+        tsp = PlainTrainer(base, momentum, predictor, opt, moco_loss, ema_update, args.moco_m, args.artifact_dir,
+                           extra_args=Namespace(moco_t=args.moco_t))
+    else:
+        tsp = TSPipe(base, momentum, predictor, opt, moco_loss, ema_update, args.moco_m, args.artifact_dir,
+                     extra_args=Namespace(moco_t=args.moco_t))
     if args.dummy or not args.data:
         loader = DummyInputGenerator(args.batch_size, input_shape=args.image, pin=torch.cuda.is_available())
     else:

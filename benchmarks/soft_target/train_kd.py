@@ -26,6 +26,7 @@ from tspipe_b200.losses import logits_kd, soft_target_kd  # noqa: E402
 from tspipe_b200.models.resnet import resnet_trunk_children, trunk_width  # noqa: E402
 from tspipe_b200.models.vit import vit_classifier  # noqa: E402
 from tspipe_b200.optim import SGD, AdamW  # noqa: E402
+from tspipe_b200.plain_trainer import PlainTrainer  # noqa: E402
 from tspipe_b200.run_log import RunLog  # noqa: E402
 
 
@@ -62,15 +63,20 @@ def main() -> None:
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--dummy", action="store_true", default=True)
     ap.add_argument("--artifact-dir", default="runs/soft_target")
+    ap.add_argument("--plain", action="store_true", help="the reference's non-pipelined trainer (one device)")
     args, _ = ap.parse_known_args()
 
     tnet, snet = create_model(args.t_name, args.num_class), create_model(args.s_name, args.num_class)
     opt = AdamW(snet.parameters(), lr=args.lr, weight_decay=0.05) if args.optimizer == "adamw" else \
         SGD(snet.parameters(), lr=args.lr, momentum=0.9, weight_decay=1e-4, nesterov=True)
-    tsp = TSPipe(snet, tnet, None, opt, soft_target_kd if args.kd_mode == "st" else logits_kd, None, 1.0,
-                 args.artifact_dir,
-                 tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False,
-                 extra_args=Namespace(T=args.T, lambda_kd=args.lambda_kd))
+    loss_fn = soft_target_kd if args.kd_mode == "st" else logits_kd
+    if args.plain:
+        tsp = PlainTrainer(snet, tnet, None, opt, loss_fn, None, 1.0, args.artifact_dir, supervised=True,
+                           target_train_mode=False, extra_args=Namespace(T=args.T, lambda_kd=args.lambda_kd))
+    else:
+        tsp = TSPipe(snet, tnet, None, opt, loss_fn, None, 1.0, args.artifact_dir,
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False,
+                     extra_args=Namespace(T=args.T, lambda_kd=args.lambda_kd))
     g = torch.Generator().manual_seed(0)
     img = torch.randn(args.batch_size, 3, args.image, args.image, generator=g)
     lab = torch.randint(0, args.num_class, (args.batch_size,), generator=g)
