@@ -25,6 +25,7 @@ from tspipe_b200.batch_ops import Batch  # noqa: E402
 from tspipe_b200.losses import distil_loss  # noqa: E402
 from tspipe_b200.models import bert as B  # noqa: E402
 from tspipe_b200.optim import AdamW  # noqa: E402
+from tspipe_b200.plain_trainer import PlainTrainer  # noqa: E402
 from tspipe_b200.run_log import RunLog  # noqa: E402
 from tspipe_b200.schedules import linear_warmup_decay  # noqa: E402
 from tspipe_b200.utils import pytree as pt  # noqa: E402
@@ -72,15 +73,21 @@ def main() -> None:
     ap.add_argument("--alpha-mlm", type=float, default=2.0)
     ap.add_argument("--alpha-cos", type=float, default=1.0)
     ap.add_argument("--artifact-dir", default="runs/distilbert")
+    ap.add_argument("--plain", action="store_true", help="the reference's non-pipelined trainer (one device)")
     args, _ = ap.parse_known_args()
     tcfg, scfg = {"bert_base": (B.BERT_BASE, B.DISTILBERT_BASE), "bert_large": (B.BERT_LARGE, B.BertConfig(
         hidden=1024, layers=12, heads=16, ffn=4096, distil=True)), "tiny": (B.BERT_TINY_TEST, B.DISTIL_TINY_TEST)}[args.teacher]
     student, teacher = B.distillation_pair(tcfg, scfg)
     opt = AdamW(student.parameters(), lr=args.lr, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.0)
-    tsp = TSPipe(student, teacher, None, opt, distil_loss, None, 1.0, args.artifact_dir,
-                 tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False, scatter_gather_fn=DICT_SG,
-                 extra_args=Namespace(temperature=args.temperature, alpha_ce=args.alpha_ce, alpha_mlm=args.alpha_mlm,
-                                      alpha_cos=args.alpha_cos))
+    extra = Namespace(temperature=args.temperature, alpha_ce=args.alpha_ce, alpha_mlm=args.alpha_mlm,
+                      alpha_cos=args.alpha_cos)
+    if args.plain:
+        tsp = PlainTrainer(student, teacher, None, opt, distil_loss, None, 1.0, args.artifact_dir, supervised=True,
+                           target_train_mode=False, scatter_gather_fn=DICT_SG, extra_args=extra)
+    else:
+        tsp = TSPipe(student, teacher, None, opt, distil_loss, None, 1.0, args.artifact_dir,
+                     tspipe_mode=TSPipeMode.SUPERVISED_MOMENTUM, target_train_mode=False, scatter_gather_fn=DICT_SG,
+                     extra_args=extra)
     g = torch.Generator().manual_seed(0)
     seq = min(args.seq_len, tcfg.max_pos)
     log = RunLog(args.artifact_dir, enabled=tsp.is_primary())      # TensorBoard scalars + scalars.csv + model.pth
