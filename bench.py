@@ -77,6 +77,8 @@ def parse(argv=None):
                    help="reference arm: as shipped (fp32), under bf16 autocast, or both")
     p.add_argument("--no-fused", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--pipeline-budget", type=int, default=300,
+                   help="seconds the secondary pipelined grids may take before the headline is printed without them")
     p.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false",
                    help="run every stage eagerly instead of replaying stage forwards / backwards from CUDA graphs")
     p.add_argument("--cuda-graphs", dest="cuda_graphs", action="store_true", help=argparse.SUPPRESS)
@@ -486,8 +488,23 @@ def run_ours(a):
         out["last_loss"] = r["last_loss"]
     if "e2e" in r:
         out["e2e"] = r["e2e"]
+    guard = None
     if placement == "colocated" and pp == 1 and not a.no_pipeline:
-        # the same job on the pipelined grids that fit this GPU count
+        # the same job on the pipelined grids that fit this GPU count.  They are secondary: if one of them should
+        # stall (a rank that failed while the others wait for it), the headline measured above is printed without
+        # them when the time budget runs out, and every rank leaves.
+        import threading
+        printed = threading.Lock()
+
+        def give_up():
+            if printed.acquire(blocking=False):
+                if rank == 0:
+                    out["pipeline_error"] = f"the pipelined grids did not finish within {a.pipeline_budget} s"
+                    print(json.dumps(out), flush=True)
+                os._exit(0)
+        guard = threading.Timer(float(a.pipeline_budget) + (0.0 if rank == 0 else 5.0), give_up)
+        guard.daemon = True
+        guard.start()
         plist = []
         for gpp, gdp, gub in pipeline_grids(world, a.workload):
             try:
@@ -500,9 +517,16 @@ def run_ours(a):
                 break
         if plist:
             out["pipeline"] = plist
+        guard.cancel()
+        if not printed.acquire(blocking=False):
+            return                              # the budget ran out a moment ago: the line is already out
     if rank == 0:
         print(json.dumps(out), flush=True)
     if dist.is_initialized():
+        import threading
+        last = threading.Timer(60.0, lambda: os._exit(0))      # the line is out: never hang in the tear-down
+        last.daemon = True
+        last.start()
         dist.barrier()
         dist.destroy_process_group()
 
