@@ -126,3 +126,24 @@ def test_split_placement_routes_cover_every_teacher_parameter_once(cut_on, cut_t
             assert torch.equal(got[o:o + p.numel()], want[i].detach().reshape(-1))
             i += 1
     assert i == len(want)
+
+
+def test_bench_cuts_and_grids_are_consistent():
+    """The benchmark's ResNet-50 cuts cover the 30 student / 26 teacher children, cut both networks at the same
+    children (so that the momentum update stays local to a stage), and its pipelined grids use every GPU."""
+    import itertools
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    from tspipe_b200.models.resnet import byol_networks
+    online, target, predictor = byol_networks("resnet50", 64, 32)
+    n_on, n_tg = len(online) + len(predictor), len(target)
+    for pp, (on, tg) in bench.BYOL_SPLITS.items():
+        assert len(on) == len(tg) == pp and sum(on) == n_on and sum(tg) == n_tg and min(on + tg) >= 1
+        assert list(itertools.accumulate(on))[:-1] == list(itertools.accumulate(tg))[:-1]
+        assert on[0] >= 4                      # conv1, bn1, relu, maxpool stay together (they run as one fused stem)
+    for world in (1, 2, 4, 8):
+        for pp, dp, ub in bench.pipeline_grids(world, "byol"):
+            assert pp * dp == world and pp in bench.BYOL_SPLITS and (128 * world // dp) % ub == 0
+    assert bench.pipeline_grids(8, "moco") == []
